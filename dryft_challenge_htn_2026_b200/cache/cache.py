@@ -38,13 +38,21 @@ class KVGroup:
         self.pool = PagePool(num_pages)
         self.pages = {}                                   # slot -> list of page ids (-1: given back)
         self.first = {}                                   # slot -> index of the first page not yet given back
-        self.store = None
-        if allocate:
+        self.store = self.v_store = None
+        vd = request.v_head_dim
+        if allocate and (vd is None or vd == request.head_dim):
             self.store = torch.zeros((len(self.entries), 2, num_pages, request.n_kv_heads, PAGE, request.head_dim),
                                      dtype=request.dtype, device=device)
+        elif allocate:    # keys and values of different sizes: a store each, [entries, pages, n_kv, PAGE, size]
+            self.store = torch.zeros((len(self.entries), num_pages, request.n_kv_heads, PAGE, request.head_dim),
+                                     dtype=request.dtype, device=device)
+            self.v_store = torch.zeros((len(self.entries), num_pages, request.n_kv_heads, PAGE, vd),
+                                       dtype=request.dtype, device=device)
 
     def view(self, entry):
         e = self.entries.index(entry)
+        if self.v_store is not None:
+            return KVView(self.index, self.store[e], self.v_store[e])
         return KVView(self.index, self.store[e, 0], self.store[e, 1])
 
     def start(self, slot):
@@ -60,11 +68,14 @@ class KVGroup:
 
     def trim(self, slot, length):
         """Gives back pages no later token can see: a query at position >= length reads keys
-        > length - window - 1 only."""
-        w = self.request.window
-        if w is None:
+        > length - window - 1 only, and with a chunk mask none before the chunk that holds position
+        ``length`` (later queries sit in that chunk or a later one)."""
+        w, c = self.request.window, self.request.chunk
+        if w is None and c is None:
             return
-        first_needed = length - w + 1
+        first_needed = 0 if w is None else length - w + 1
+        if c is not None:
+            first_needed = max(first_needed, length // c * c)
         have = self.pages[slot]
         i = self.first[slot]
         while i < len(have) and i * PAGE + PAGE - 1 < first_needed:
@@ -78,7 +89,7 @@ class KVGroup:
         del self.first[slot]
 
     def bytes(self):
-        return 0 if self.store is None else self.store.numel() * self.store.element_size()
+        return sum(t.numel() * t.element_size() for t in (self.store, self.v_store) if t is not None)
 
 
 class StateGroup:

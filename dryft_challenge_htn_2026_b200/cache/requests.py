@@ -7,12 +7,17 @@ import torch
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values per token: [n_kv_heads, head_dim] each. ``window``: only the last
-    ``window`` tokens are ever read, older pages may be given back; None: all tokens are kept."""
+    """Keys and values per token: [n_kv_heads, head_dim] each (values [n_kv_heads, v_head_dim] when
+    that is given and differs: the two then live in stores of their own). ``window``: only the last
+    ``window`` tokens are ever read, older pages may be given back; None: all tokens are kept.
+    ``chunk``: a token reads only keys of its own chunk of that many positions (counted from the
+    sequence's start), so pages wholly before the chunk of the next token may be given back."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int]
     dtype: torch.dtype
+    v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -1,8 +1,12 @@
 """Typed configuration: part specifications, the model specification built from them, and the
 architecture's own config.json reader."""
-from .specs import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, RMSNormSpec, RotaryHalfSpec, ScheduleEntry)
+from .specs import (AttentionSpec, DenseMLPSpec, GatedMLPSpec, LayerSpec, LinearAttentionSpec, MaskedAttentionSpec,
+                    ModelSpec, ParallelMixerSpec, RMSNormSpec, RotaryHalfSpec, ScalarRMSNormSpec, ScheduleEntry,
+                    SinusoidSpec)
 from .base import ConfigError, ModelConfig
+from .nilivik import NilivikConfig
 from .qwen3 import Qwen3Config
 
-__all__ = ["AttentionSpec", "GatedMLPSpec", "LayerSpec", "ModelSpec", "RMSNormSpec", "RotaryHalfSpec",
-           "ScheduleEntry", "ConfigError", "ModelConfig", "Qwen3Config"]
+__all__ = ["AttentionSpec", "DenseMLPSpec", "GatedMLPSpec", "LayerSpec", "LinearAttentionSpec", "MaskedAttentionSpec",
+           "ModelSpec", "ParallelMixerSpec", "RMSNormSpec", "RotaryHalfSpec", "ScalarRMSNormSpec", "ScheduleEntry",
+           "SinusoidSpec", "ConfigError", "ModelConfig", "NilivikConfig", "Qwen3Config"]

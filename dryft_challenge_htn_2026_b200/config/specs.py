@@ -18,6 +18,21 @@ class RMSNormSpec:
 
 
 @dataclass(frozen=True)
+class ScalarRMSNormSpec:
+    """y = g * x * rsqrt(mean(x^2) + eps) with one learned number g for all ``dim`` coordinates."""
+    dim: int
+    eps: float
+
+
+@dataclass(frozen=True)
+class SinusoidSpec:
+    """Absolute position vector added to the embedding: entry 2i = sin(p * base^(-2i/dim)), entry
+    2i+1 = cos of the same angle."""
+    dim: int
+    base: float = 10000.0
+
+
+@dataclass(frozen=True)
 class RotaryHalfSpec:
     """Rotate-half rotary encoding over the whole head: angle(p, j) = p * theta^(-2j/dim)."""
     dim: int
@@ -38,6 +53,59 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class MaskedAttentionSpec:
+    """Causal grouped-query softmax attention without rotation, with options: value heads of a size
+    of their own; a chunk mask (position i sees j <= i only if floor(i / chunk) == floor(j / chunk),
+    chunks counted from the sequence's first position) and/or a sliding window; a logarithmic distance
+    bias taken off the score, r1_h * ln(1 + r2_h * (i - j)), with two learned numbers a head; a sink (a
+    learned number a head whose exponential joins the softmax's denominator and nothing else); an
+    output gate sigmoid(W_g x) on the concatenated heads before the output projection."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    chunk: Optional[int] = None
+    window: Optional[int] = None
+    distance_bias: bool = False
+    sink: bool = False
+    output_gate: bool = False
+
+
+@dataclass(frozen=True)
+class LinearAttentionSpec:
+    """Linear attention with a constant decay per head: q, k, v = silu(W x); per head
+    S_t = decay_h * S_(t-1) + k_t v_t^T (state [head_dim, v_head_dim], float32, zero at the start),
+    o_t = S_t^T q_t; all heads together through ``out_norm`` (a weighted RMS norm over
+    num_heads * v_head_dim), times sigmoid(W_g x) when ``output_gate``, then the output projection."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    decay: Tuple[float, ...]
+    out_norm: Any = None
+    output_gate: bool = True
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side on the same input; the result is the sum of scale_i * mixer_i(x).
+    ``branches``: (checkpoint prefix under the mixer, mixer spec, scale) each."""
+    hidden_size: int
+    branches: Tuple[Tuple[str, Any, float], ...]
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """down(act(up(x))) without bias. ``activation`` "xielu": with two learned numbers p, q,
+    act(z) = softplus(p) z^2 + z/2 for z > 0 and (1/2 + softplus(q)) (e^z - 1 - z) + z/2 otherwise."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "xielu"
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
     """down(act(gate(x)) * up(x)) without bias."""
     hidden_size: int
@@ -48,7 +116,8 @@ class GatedMLPSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One pre-norm residual block: h += mixer(norm_in(h)); h += feed_forward(norm_post(h)).
-    ``prefix`` is the layer's tensor-name prefix in the checkpoint."""
+    ``prefix`` is the layer's tensor-name prefix in the checkpoint. A layer without a feed-forward has
+    ``norm_post`` and ``feed_forward`` None (and no names for them)."""
     prefix: str
     norm_in: Any
     mixer: Any
@@ -62,10 +131,14 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer. ``cache`` names the cache entry the layer's mixer uses; with
-    ``writes=False`` the mixer only reads what the entry's owner stored in this step."""
+    ``writes=False`` the mixer only reads what the entry's owner stored in this step. Right before the
+    run the residual stream may take in the embedding's output once more (``add_embedding``) and a row
+    of a learned table of the model (``add_row`` = (name in ``ModelSpec.tables``, row))."""
     layer: int
     cache: int
     writes: bool = True
+    add_embedding: bool = False
+    add_row: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -81,6 +154,10 @@ class ModelSpec:
     embed_name: str = "model.embed_tokens.weight"
     final_norm_prefix: str = "model.norm."
     head_name: str = "lm_head.weight"
+    embed_scale: float = 1.0                   # multiplies the embedding row
+    embed_position: Optional[Any] = None       # position spec whose vector is added to the embedding
+    logit_cap: Optional[float] = None          # logits <- cap * tanh(logits / cap)
+    tables: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()   # learned float32 tables of the model itself: (checkpoint name, shape)
     extra: dict = field(default_factory=dict, compare=False)
 
     @staticmethod

@@ -602,3 +602,129 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
                                        c_float(scale), _p(_tc_err), _p(sched), c_void_p(stream)), "attention_prefill_tc")
 
+
+
+# ------------------------------------------------------ embedding with position, stream adds, caps
+def _need_rows(t, name, dtype=None):
+    """A 2-d CUDA tensor whose rows are contiguous (the rows themselves may lie in a wider matrix)."""
+    if t is None:
+        return
+    if not t.is_cuda or t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be a 2-d CUDA tensor with contiguous rows")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def embed_position_rmsnorm(tok, embed, scale, row_pos, inv_freq, norm_w, eps, h_out, a_out):
+    """h_out[t] = embed[tok[t]] * scale + sinusoid(row_pos[t]) (float32; the sinusoid only with
+    ``inv_freq``, float64 [H/2]: sine of position * inv_freq[i] at 2i, cosine at 2i+1);
+    a_out[t] = rmsnorm(h_out[t]) * norm_w when norm_w is given."""
+    _need(tok, "tok", torch.int32, 1), _need(embed, "embed", None, 2), _need(norm_w, "norm_w", torch.float32, 1)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(inv_freq, "inv_freq", torch.float64, 1)
+    _need(h_out, "h_out", torch.float32, 2), _need(a_out, "a_out", embed.dtype, 2)
+    n, (V, H) = tok.numel(), embed.shape
+    if inv_freq is not None and (inv_freq.numel() != H // 2 or row_pos is None or row_pos.numel() < n):
+        raise KernelError(f"embed_position_rmsnorm: {inv_freq.numel()} frequencies for width {H}, or positions missing")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_embed_position_rmsnorm(_dt(embed), _p(tok), _p(embed), c_float(scale), _p(row_pos), _p(inv_freq),
+                                              _p(norm_w), c_float(eps), n, H, V, _p(h_out), _p(a_out), _stream()),
+           "embed_position_rmsnorm")
+
+
+def stream_add(h, other=None, vec=None):
+    """h += other (float32, h's shape) + vec (float32 [H]), whichever is given."""
+    _need(h, "h", torch.float32, 2), _need(other, "other", torch.float32, 2), _need(vec, "vec", torch.float32, 1)
+    if (other is not None and other.shape != h.shape) or (vec is not None and vec.numel() != h.shape[1]):
+        raise KernelError("stream_add: shapes do not match")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_stream_add(_p(h), _p(other), _p(vec), c_longlong(h.shape[0]), h.shape[1], _stream()), "stream_add")
+
+
+def softcap(x, cap):
+    """x = cap * tanh(x / cap) in place (float32)."""
+    _need(x, "x", torch.float32)
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_softcap(_p(x), c_longlong(x.numel()), c_float(cap), _stream()), "softcap")
+
+
+def xielu(z, out, alpha_pos, alpha_neg):
+    """out = alpha_pos z^2 + z/2 (z > 0), alpha_neg (e^z - 1 - z) + z/2 (z <= 0)."""
+    _need(z, "z", None), _need(out, "out", z.dtype)
+    if out.shape != z.shape:
+        raise KernelError("xielu: shapes do not match")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_xielu(_dt(z), _p(z), _p(out), c_longlong(z.numel()), c_float(alpha_pos), c_float(alpha_neg),
+                             _stream()), "xielu")
+
+
+# ------------------------------------------------------------- attention with mask, bias and sink
+def kv_write(k, v, k_store, v_store, row_pos, row_seq, page_table, n_kv_heads, head_dim, v_head_dim):
+    """k [T, nkv*hd] and v [T, nkv*hdv] (rows of a wider matrix, one common row stride) into the paged
+    stores [pages, nkv, PAGE, hd] / [pages, nkv, PAGE, hdv] at each token's position."""
+    _need_rows(k, "k"), _need_rows(v, "v", k.dtype)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", k.dtype), _need(v_store, "v_store", k.dtype)
+    if k.stride(0) != v.stride(0) or k.shape[1] != n_kv_heads * head_dim or v.shape[1] != n_kv_heads * v_head_dim:
+        raise KernelError("kv_write: k and v must be rows of one matrix, nkv*hd and nkv*hdv wide")
+    lib = _lib("attention_masked.cu")
+    _check(lib, lib.dk_kv_write(_dt(k), _p(k), _p(v), c_longlong(k.stride(0)), _p(k_store), _p(v_store), _p(row_pos),
+                                _p(row_seq), _p(page_table), page_table.shape[1], k.shape[0], n_kv_heads, head_dim,
+                                v_head_dim, _stream()), "kv_write")
+
+
+def attention_masked(q, out, gate, out_scale, k_store, v_store, row_pos, row_seq, page_table, n_heads, n_kv_heads,
+                     head_dim, v_head_dim, window, chunk, scale, r1=None, r2=None, sink=None):
+    """Float32-arithmetic attention of every token row over its sequence's cached keys: causal, inside
+    the row's chunk (``chunk`` positions, 0: none) and window (0: none); score = q.k * scale
+    - r1_h * ln(1 + r2_h * distance) (with r1, r2 float32 [nh]); exp(sink_h) joins the denominator (with
+    sink); out = heads * sigmoid(gate) (with gate) * out_scale. q, gate and out may be rows of wider
+    matrices. Any phase; float32 or bfloat16 storage."""
+    _need_rows(q, "q"), _need_rows(out, "out", q.dtype), _need_rows(gate, "gate", q.dtype)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", q.dtype), _need(v_store, "v_store", q.dtype)
+    _need(r1, "r1", torch.float32, 1), _need(r2, "r2", torch.float32, 1), _need(sink, "sink", torch.float32, 1)
+    if head_dim > 256 or v_head_dim > 256 or n_heads % n_kv_heads or (r1 is None) != (r2 is None):
+        raise KernelError(f"attention_masked: head sizes {head_dim}/{v_head_dim} (max 256), heads {n_heads}:{n_kv_heads}")
+    if q.shape[1] != n_heads * head_dim or out.shape[1] != n_heads * v_head_dim or \
+            (gate is not None and gate.shape[1] != n_heads * v_head_dim):
+        raise KernelError("attention_masked: q, gate or out of the wrong width")
+    lib = _lib("attention_masked.cu")
+    _check(lib, lib.dk_attention_masked(_dt(q), _p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)),
+                                        _p(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                        c_float(out_scale), _p(k_store), _p(v_store), _p(row_pos), _p(row_seq),
+                                        _p(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
+                                        v_head_dim, int(window or 0), int(chunk or 0), c_float(scale), _p(r1), _p(r2),
+                                        _p(sink), _stream()), "attention_masked")
+
+
+# ------------------------------------------------------------------------ decayed linear attention
+def linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim):
+    """The recurrence S <- d_h S + silu(k) silu(v)^T, o = S^T silu(q), token by token, for the token rows
+    [cu_q[s], cu_q[s+1]) of each sequence (``cu_q`` None: row s alone); state float32
+    [slots, nh, hd, hdv] at row seq_slot[s], read and written back; out float32 [T, nh*hdv]. A sequence
+    with seq_pos0[s] < 0 is padding (zeros out, state untouched)."""
+    _need_rows(q, "q"), _need_rows(k, "k", q.dtype), _need_rows(v, "v", q.dtype)
+    _need(out, "out", torch.float32, 2), _need(state, "state", torch.float32, 4), _need(decay, "decay", torch.float32, 1)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.shape[1] != n_heads * head_dim or \
+            v.shape[1] != n_heads * v_head_dim or tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or \
+            decay.numel() != n_heads or head_dim > 256 or v_head_dim > 256:
+        raise KernelError("linear_attention_step: shapes do not match (head sizes up to 256)")
+    lib = _lib("linear_attention.cu")
+    _check(lib, lib.dk_linear_attention_step(_dt(q), _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out), _p(state),
+                                             _p(cu_q), _p(seq_pos0), _p(seq_slot), _p(decay), n_seq, n_heads, head_dim,
+                                             v_head_dim, _stream()), "linear_attention_step")
+
+
+def norm_gate(o, weight, eps, gate, out_scale, out):
+    """out = rmsnorm(o) * weight * sigmoid(gate) * out_scale, the norm over each whole row of o
+    (float32 [T, n]); gate and out in the storage type, possibly rows of wider matrices."""
+    _need(o, "o", torch.float32, 2), _need(weight, "weight", torch.float32, 1)
+    _need_rows(gate, "gate", out.dtype), _need_rows(out, "out")
+    n = o.shape[1]
+    if weight.numel() != n or out.shape != o.shape or (gate is not None and gate.shape != o.shape):
+        raise KernelError("norm_gate: shapes do not match")
+    lib = _lib("linear_attention.cu")
+    _check(lib, lib.dk_norm_gate(_dt(out), _p(o), _p(weight), c_float(eps), _p(gate),
+                                 c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale), _p(out),
+                                 c_longlong(out.stride(0)), o.shape[0], n, _stream()), "norm_gate")

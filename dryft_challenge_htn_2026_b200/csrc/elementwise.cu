@@ -575,3 +575,111 @@ DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* par
 DK_EXPORT int dk_gather_rows_f32(const float* src, const int* rows, float* out, int n_rows, int H, cudaStream_t st) {
     return dk_launch(gather_rows_f32_kernel, dim3(n_rows), dim3(256), 0, st, src, rows, out, H);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Embedding with a scale and an absolute sinusoidal position vector:
+//   h[row][2i] = embed[tok][2i] * scale + sin(p * f_i),  h[row][2i+1] = embed[tok][2i+1] * scale + cos(p * f_i)
+// with p the row's position and f_i = inv_freq[i] (float64, made on the host). The angle is formed and
+// brought into [-pi, pi] in float64, so that it is right to float32 rounding at any position; sine and
+// cosine are the float32 functions. Without a table (inv_freq == nullptr) only the scale applies.
+// a[row] = rmsnorm(h[row]) * w when w is given. Rows with position < 0 (padding) get position 0.
+template <typename T>
+__global__ void embed_position_rmsnorm_kernel(const int* tok, const T* __restrict__ embed, float scale,
+                                              const int* row_pos, const double* __restrict__ inv_freq,
+                                              const float* __restrict__ w, float eps, int H, int V, float* h, T* a) {
+    __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    int t = tok[row];
+    t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+    const int p = inv_freq ? max(row_pos[row], 0) : 0;
+    const T* e = embed + (size_t)t * H;
+    float* hr = h + row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_f(e[i]) * scale;
+        if (inv_freq && (i >> 1) < H / 2) {
+            double ang = (double)p * inv_freq[i >> 1];
+            ang -= 6.283185307179586476925 * rint(ang * 0.15915494309189533577);
+            v += (i & 1) ? cosf((float)ang) : sinf((float)ang);
+        }
+        hr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    if (w == nullptr) return;
+    const float rs = rsqrtf(ss / (float)H + eps);
+    T* ar = a + row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(hr[i] * rs * w[i]);
+}
+
+DK_EXPORT int dk_embed_position_rmsnorm(int dtype, const int* tok, const void* embed, float scale, const int* row_pos,
+                                        const double* inv_freq, const float* w, float eps, int n_tok, int H, int V,
+                                        float* h, void* a, cudaStream_t st) {
+    DISPATCH_T(dtype, return dk_launch(embed_position_rmsnorm_kernel<T>, dim3(n_tok), dim3(row_threads(H)), 0, st, tok,
+                                       (const T*)embed, scale, row_pos, inv_freq, w, eps, H, V, h, (T*)a));
+}
+
+// h[row] += other[row] (if other) + vec (if vec): what a schedule adds to the residual stream before a
+// layer (a saved copy of the stream, a learned vector). All float32.
+__global__ void stream_add_kernel(float* h, const float* other, const float* __restrict__ vec, size_t n, int H) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = h[i];
+    if (other) v += other[i];
+    if (vec) v += vec[i % H];
+    h[i] = v;
+}
+
+DK_EXPORT int dk_stream_add(float* h, const float* other, const float* vec, long long n_rows, int H, cudaStream_t st) {
+    const size_t n = (size_t)n_rows * H;
+    return dk_launch(stream_add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, h, other, vec, n, H);
+}
+
+// x = cap * tanh(x / cap) in place (float32 logits)
+__global__ void softcap_kernel(float* x, size_t n, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+DK_EXPORT int dk_softcap(float* x, long long n, float cap, cudaStream_t st) {
+    return dk_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, (size_t)n, cap);
+}
+
+// xIELU: f(z) = ap z^2 + z/2 for z > 0, an (e^z - 1 - z) + z/2 otherwise; arithmetic in float32.
+__device__ __forceinline__ float xielu_f(float z, float ap, float an) {
+    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+}
+
+template <typename T>
+__global__ void xielu_kernel(const T* z, T* out, size_t n, float ap, float an) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f<T>(xielu_f(to_f(z[i]), ap, an));
+}
+
+__global__ void xielu_wide_kernel(const bf16* z, bf16* out, size_t n8, float ap, float an) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    uint4 raw = reinterpret_cast<const uint4*>(z)[i];
+    bf16* v = reinterpret_cast<bf16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = __float2bfloat16_rn(xielu_f(__bfloat162float(v[k]), ap, an));
+    reinterpret_cast<uint4*>(out)[i] = raw;
+}
+
+DK_EXPORT int dk_xielu(int dtype, const void* z, void* out, long long n, float ap, float an, cudaStream_t st) {
+    if (dtype == 1 && n % 8 == 0 && ((uintptr_t)z % 16 == 0) && ((uintptr_t)out % 16 == 0))
+        return dk_launch(xielu_wide_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, (const bf16*)z,
+                         (bf16*)out, (size_t)(n / 8), ap, an);
+    DISPATCH_T(dtype, return dk_launch(xielu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const T*)z,
+                                       (T*)out, (size_t)n, ap, an));
+}

@@ -36,6 +36,15 @@ class CausalLM:
         self._entry_requests = [self.blocks[owners[c]].cache_requests() for c in range(n_entries)]
         self.embed = self.head = None
         self.tied = None
+        self.position = build_part(spec.embed_position, self.rt) if spec.embed_position is not None else None
+        if self.position is not None and not getattr(self.position, "added_to_embedding", False):
+            raise TypeError(f"{type(self.position).__name__} is not a position vector the embedding can add")
+        self.tables = {}         # the model's own learned tables (ModelSpec.tables), float32, by name
+        names = {n for n, _ in spec.tables}
+        for e in spec.schedule:
+            if e.add_row is not None and e.add_row[0] not in names:
+                raise ValueError(f"schedule adds a row of {e.add_row[0]!r}, which is not a table of the model")
+        self._keeps_embedding = any(e.add_embedding for e in spec.schedule)
         # index arrays the parts' kernels want built for every step (engine.batch.build_context), once per key
         self.step_plans = list({p.key: p for b in self.blocks for p in b.step_plans()}.values())
         self.prepared = 0        # positions the parts' tables reach
@@ -51,6 +60,8 @@ class CausalLM:
                 out[ls.prefix + p.name] = p
         for p in self.final_norm.param_decls():
             out[s.final_norm_prefix + p.name] = p
+        for name, shape in s.tables:
+            out[name] = ParamDecl(name, tuple(shape), "matrix", keep_float32=True)
         if not tied:
             out[s.head_name] = ParamDecl(s.head_name, (s.vocab_size, s.hidden_size), "matrix")
         return out
@@ -60,6 +71,7 @@ class CausalLM:
         self.tied = tied
         self.embed = tensors.pop(s.embed_name).contiguous()
         self.head = self.embed if tied else tensors.pop(s.head_name).contiguous()
+        self.tables = {name: tensors.pop(name).to(torch.float32).contiguous() for name, _ in s.tables}
         for ls, blk in zip(s.layers, self.blocks):
             n = len(ls.prefix)
             blk.bind({k[n:]: tensors.pop(k) for k in [k for k in tensors if k.startswith(ls.prefix)]})
@@ -97,11 +109,20 @@ class CausalLM:
         h = torch.empty((ctx.n_tok, s.hidden_size), dtype=torch.float32, device=rt.device)
         a = torch.empty((ctx.n_tok, s.hidden_size), dtype=rt.dtype, device=rt.device)
         first = self.blocks[s.schedule[0].layer]
-        fused = isinstance(first.norm_in, RMSNorm)       # the embedding kernel computes RMSNorm and nothing else
-        api.embed_rmsnorm(ctx.tok, self.embed, first.norm_in.weight if fused else None,
-                          first.norm_in.spec.eps if fused else 0.0, h, a)
+        # the embedding kernel computes RMSNorm and nothing else, and only of the embedding as it leaves the kernel
+        fused = isinstance(first.norm_in, RMSNorm) and not (s.schedule[0].add_embedding or s.schedule[0].add_row)
+        norm_w, eps = (first.norm_in.weight, first.norm_in.spec.eps) if fused else (None, 0.0)
+        if self.position is None and s.embed_scale == 1.0:
+            api.embed_rmsnorm(ctx.tok, self.embed, norm_w, eps, h, a)
+        else:
+            api.embed_position_rmsnorm(ctx.tok, self.embed, s.embed_scale, ctx.row_pos,
+                                       self.position.inv_freq if self.position is not None else None, norm_w, eps, h, a)
+        e0 = h.clone() if self._keeps_embedding else None     # the embedding's output, for the runs that take it in again
         pending = None
         for i, e in enumerate(s.schedule):
+            if e.add_embedding or e.add_row is not None:
+                api.stream_add(h, e0 if e.add_embedding else None,
+                               self.tables[e.add_row[0]][e.add_row[1]] if e.add_row is not None else None)
             pending = self.blocks[e.layer].forward(ctx, h, pending, cache.views(e.cache), e.writes,
                                                    a if (i == 0 and fused) else None)
             if tap is not None:
@@ -109,4 +130,7 @@ class CausalLM:
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
         an = add_norm(self.final_norm, h, pending, rt.dtype, rows=ctx.want_rows)
-        return linear(an, self.head, STORE_F32)
+        logits = linear(an, self.head, STORE_F32)
+        if s.logit_cap:
+            api.softcap(logits, s.logit_cap)
+        return logits

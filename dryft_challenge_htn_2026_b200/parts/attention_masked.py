@@ -1,0 +1,91 @@
+"""Grouped-query softmax attention without rotation over the paged cache, with a chunk mask or a
+window, a logarithmic distance bias, a sink in the softmax's denominator and an output gate, each
+switched on by its specification; key and value heads may differ in size.
+
+forward = one fused projection [q; k; v; gate] -> k and v into the cache -> attention over the cache
+with the gate in its epilogue -> output projection. The part also runs as a branch of a
+``ParallelMixer``, which does the projections of all its branches in one product each: ``mix`` takes
+the projected rows and leaves scale * (gated heads) where the caller wants them.
+"""
+import torch
+
+from ..cache.requests import KVRequest
+from ..config.specs import MaskedAttentionSpec
+from ..csrc import api
+from .base import ParamDecl, Part, register_part
+from .linear import linear
+
+
+class MaskedAttention(Part):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError(f"{s.num_heads} query heads are not a multiple of {s.num_kv_heads} key/value heads")
+        if max(s.head_dim, s.v_head_dim) > 256:
+            raise ValueError(f"attention kernels take head sizes up to 256, not {s.head_dim} / {s.v_head_dim}")
+        if s.chunk is not None and s.chunk < 1:
+            raise ValueError(f"a chunk of {s.chunk} positions")
+        self.n_q, self.n_k = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        self.n_v, self.n_mid = s.num_kv_heads * s.v_head_dim, s.num_heads * s.v_head_dim
+        self.n_in = self.n_q + self.n_k + self.n_v + (self.n_mid if s.output_gate else 0)
+        if rt.dtype == torch.bfloat16 and (s.hidden_size % 8 or self.n_mid % 8):
+            raise ValueError("bfloat16 projections need inner sizes that are multiples of 8, not "
+                             f"{s.hidden_size} / {self.n_mid}")
+        self.r1 = self.r2 = self.sink = None
+
+    def param_decls(self):
+        s = self.spec
+        d = [ParamDecl("q", (self.n_q, s.hidden_size)), ParamDecl("k", (self.n_k, s.hidden_size)),
+             ParamDecl("v", (self.n_v, s.hidden_size)), ParamDecl("o", (s.hidden_size, self.n_mid))]
+        if s.output_gate:
+            d.append(ParamDecl("g", (self.n_mid, s.hidden_size)))
+        if s.distance_bias:
+            d += [ParamDecl("r1", (s.num_heads,), init="positive", keep_float32=True),
+                  ParamDecl("r2", (s.num_heads,), init="positive", keep_float32=True)]
+        if s.sink:
+            d.append(ParamDecl("sink", (s.num_heads,), init="unit", keep_float32=True))
+        return d
+
+    def bind(self, tensors):
+        rows = [tensors.pop("q"), tensors.pop("k"), tensors.pop("v")]
+        if self.spec.output_gate:
+            rows.append(tensors.pop("g"))
+        self.w_in = torch.cat(rows, 0).contiguous()
+        self.w_o = tensors.pop("o").contiguous()
+        if self.spec.distance_bias:
+            self.r1 = tensors.pop("r1").to(torch.float32).contiguous()
+            self.r2 = tensors.pop("r2").to(torch.float32).contiguous()
+        if self.spec.sink:
+            self.sink = tensors.pop("sink").to(torch.float32).contiguous()
+
+    def step_weights(self):
+        return [self.w_in, self.w_o]
+
+    def cache_requests(self):
+        s = self.spec
+        return [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype, s.v_head_dim, s.chunk)]
+
+    def mix(self, ctx, views, proj, mid, scale, writes=True):
+        """``proj`` [tokens, n_in]: this part's rows of a projection (possibly columns of a wider matrix);
+        ``mid`` [tokens, n_mid]: where scale * (gated heads) go."""
+        s, kv = self.spec, views[0]
+        table = ctx.tables[kv.group]
+        q = proj[:, :self.n_q]
+        k = proj[:, self.n_q:self.n_q + self.n_k]
+        v = proj[:, self.n_q + self.n_k:self.n_q + self.n_k + self.n_v]
+        gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
+        if writes:
+            api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
+        api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_heads,
+                             s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale, self.r1, self.r2,
+                             self.sink)
+
+    def forward(self, ctx, views, a, writes=True):
+        proj = linear(a, self.w_in)
+        mid = torch.empty((ctx.n_tok, self.n_mid), dtype=self.rt.dtype, device=self.rt.device)
+        self.mix(ctx, views, proj, mid, 1.0, writes)
+        return linear(mid, self.w_o, allow_partial=True)
+
+
+register_part(MaskedAttentionSpec, MaskedAttention)

@@ -18,11 +18,12 @@ class PreNormBlock(Part):
         super().__init__(spec, rt)
         self.norm_in = build_part(spec.norm_in, rt)
         self.mixer = build_part(spec.mixer, rt)
-        self.norm_post = build_part(spec.norm_post, rt)
-        self.feed_forward = build_part(spec.feed_forward, rt)
+        # a layer may go without a feed-forward: then the mixer's output is what it hands on
+        self.norm_post = build_part(spec.norm_post, rt) if spec.feed_forward is not None else None
+        self.feed_forward = build_part(spec.feed_forward, rt) if spec.feed_forward is not None else None
 
     def _subparts(self):
-        return [(getattr(self, attr), pre) for attr, pre in self.spec.names]
+        return [(getattr(self, attr), pre) for attr, pre in self.spec.names if getattr(self, attr) is not None]
 
     def param_decls(self):
         return [ParamDecl(pre + p.name, p.shape, p.init, p.keep_float32) for part, pre in self._subparts()
@@ -52,6 +53,8 @@ class PreNormBlock(Part):
         if a is None:
             a = add_norm(self.norm_in, h, pending, self.rt.dtype)
         d = self.mixer.forward(ctx, views, a, writes)
+        if self.feed_forward is None:
+            return d
         a = add_norm(self.norm_post, h, d, self.rt.dtype)
         return self.feed_forward.forward(ctx, a)
 

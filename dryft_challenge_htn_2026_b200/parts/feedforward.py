@@ -1,7 +1,10 @@
 """Dense gated feed-forward: down(silu(gate(x)) * up(x)) (reference: engine/engine.py:137-146,494-495)."""
+import math
+
 import torch
 
-from ..config.specs import GatedMLPSpec
+from ..config.specs import DenseMLPSpec, GatedMLPSpec
+from ..csrc import api
 from .base import ParamDecl, Part, register_part
 from .linear import SILU, linear
 
@@ -34,3 +37,41 @@ class GatedMLP(Part):
 
 
 register_part(GatedMLPSpec, GatedMLP)
+
+
+class DenseMLP(Part):
+    """down(act(up(x))) with the xIELU activation: act(z) = ap z^2 + z/2 for z > 0 and
+    an (e^z - 1 - z) + z/2 otherwise, ap = softplus(p), an = 1/2 + softplus(q) from the two learned
+    numbers of ``act`` (worked out once, in float64, when the tensors are bound). In the float32 path and
+    in decode steps the activation is a kernel of its own between the two products."""
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if spec.activation != "xielu":
+            raise ValueError(f"activation {spec.activation!r} is not implemented (xielu only)")
+        if rt.dtype == torch.bfloat16 and (spec.hidden_size % 8 or spec.intermediate_size % 8):
+            raise ValueError("bfloat16 products need hidden and intermediate sizes that are multiples of 8, "
+                             f"not {spec.hidden_size} / {spec.intermediate_size}")
+
+    def param_decls(self):
+        s = self.spec
+        return [ParamDecl("up", (s.intermediate_size, s.hidden_size)), ParamDecl("down", (s.hidden_size, s.intermediate_size)),
+                ParamDecl("act", (2,), init="unit", keep_float32=True)]
+
+    def bind(self, tensors):
+        self.w_up = tensors.pop("up").contiguous()
+        self.w_down = tensors.pop("down").contiguous()
+        p, q = (float(x) for x in tensors.pop("act").to(torch.float64).cpu())
+        softplus = lambda x: max(x, 0.0) + math.log1p(math.exp(-abs(x)))
+        self.alpha_pos, self.alpha_neg = softplus(p), 0.5 + softplus(q)
+
+    def step_weights(self):
+        return [self.w_up, self.w_down]
+
+    def forward(self, ctx, a):
+        z = linear(a, self.w_up)
+        api.xielu(z, z, self.alpha_pos, self.alpha_neg)
+        return linear(z, self.w_down, allow_partial=True)
+
+
+register_part(DenseMLPSpec, DenseMLP)

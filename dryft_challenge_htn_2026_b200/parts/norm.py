@@ -1,7 +1,7 @@
 """RMSNorm (reference: engine/engine.py:107-110, engine/fused.py:152-172)."""
 import torch
 
-from ..config.specs import RMSNormSpec
+from ..config.specs import RMSNormSpec, ScalarRMSNormSpec
 from ..csrc import api
 from .base import ParamDecl, Part, register_part
 
@@ -24,3 +24,20 @@ class RMSNorm(Part):
 
 
 register_part(RMSNormSpec, RMSNorm)
+
+
+class ScalarRMSNorm(RMSNorm):
+    """RMS norm with one learned number for all coordinates: y = g * x * rsqrt(mean(x^2) + eps). The
+    number is spread over the width when it is bound, so the norm runs on the kernels of ``RMSNorm``
+    (fused with the residual add, with the embedding, gathered at the wanted rows). Its tensor has no
+    name of its own under the part's prefix: the prefix is the tensor's name."""
+
+    def param_decls(self):
+        return [ParamDecl("", (), init="norm", keep_float32=True)]
+
+    def bind(self, tensors):
+        self.gain = tensors[""].to(torch.float32).reshape(())
+        self.weight = self.gain.expand(self.spec.dim).contiguous()
+
+
+register_part(ScalarRMSNormSpec, ScalarRMSNorm)

@@ -10,7 +10,7 @@ cache write and cannot be combined with a per-head q/k norm (which would have to
 attention part refuses that pair."""
 import torch
 
-from ..config.specs import RotaryHalfSpec
+from ..config.specs import RotaryHalfSpec, SinusoidSpec
 from .base import Part, register_part
 
 
@@ -34,3 +34,18 @@ class RotaryHalf(Part):
 
 
 register_part(RotaryHalfSpec, RotaryHalf)
+
+
+class Sinusoid(Part):
+    """Absolute sinusoidal position vector, added to the embedding by the embedding kernel. The part
+    owns the frequencies base^(-2i/dim), worked out in float64 on the host; the kernel forms
+    position * frequency in float64 too, so the angle is right to float32 rounding at any position."""
+    added_to_embedding = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        i = torch.arange(spec.dim // 2, dtype=torch.float64)
+        self.inv_freq = (float(spec.base) ** (-2.0 * i / spec.dim)).to(rt.device)
+
+
+register_part(SinusoidSpec, Sinusoid)

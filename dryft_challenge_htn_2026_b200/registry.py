@@ -4,6 +4,7 @@ class. The config class turns config.json into a ``ModelSpec``; the parts regist
 Adding an architecture: write a ``ModelConfig`` subclass with ``architecture``, ``from_dict``,
 ``to_dict`` and ``to_spec``, then ``register_architecture(YourConfig)``."""
 from .config.base import ConfigError, read_config_json
+from .config.nilivik import NilivikConfig
 from .config.qwen3 import Qwen3Config
 
 _ARCHITECTURES = {}
@@ -29,8 +30,10 @@ def config_class(name):
 
 def config_from_dict(d):
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):     # some designs name one architecture, not a list
+        archs = [d["architecture"]]
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
-        raise ConfigError(f"config.json: 'architectures' must be a list with one name, got {archs!r}")
+        raise ConfigError(f"config.json: 'architectures' must be a list with one name (or 'architecture' a name), got {archs!r}")
     return config_class(archs[0]).from_dict(d)
 
 
@@ -39,3 +42,4 @@ def config_from_folder(folder):
 
 
 register_architecture(Qwen3Config)
+register_architecture(NilivikConfig)

@@ -10,6 +10,19 @@ from safetensors.torch import save_file
 from ..engine.model import CausalLM
 
 
+def _shape_draw(x, init, matrix_std, norm_std):
+    """A standard normal draw turned into the kind of parameter ``init`` names: "matrix" N(0, matrix_std),
+    "norm" 1 + N(0, norm_std), "unit" N(0, 1) (free numbers: sinks, activation shapes), "positive"
+    0.05 + |N(0, 0.3)| (rates that multiply a distance)."""
+    if init == "norm":
+        return 1.0 + norm_std * x
+    if init == "unit":
+        return x
+    if init == "positive":
+        return 0.05 + 0.3 * x.abs()
+    return matrix_std * x
+
+
 def random_tensors(config, seed, dtype=torch.bfloat16, matrix_std=0.02, norm_std=0.1):
     spec = config.to_spec()
     tied = bool(spec.tie_embeddings)
@@ -18,7 +31,7 @@ def random_tensors(config, seed, dtype=torch.bfloat16, matrix_std=0.02, norm_std
     out = {}
     for name, decl in sorted(shell.param_decls(tied).items()):
         x = torch.randn(decl.shape, generator=gen, dtype=torch.float32)
-        x = 1.0 + norm_std * x if decl.init == "norm" else matrix_std * x
+        x = _shape_draw(x, decl.init, matrix_std, norm_std)
         out[name] = x.to(dtype).contiguous()
     return out
 
@@ -40,7 +53,7 @@ def bind_random(model, seed=0, matrix_std=0.02, norm_std=0.1):
     tensors = {}
     for name, decl in sorted(model.param_decls(tied).items()):
         x = torch.randn(decl.shape, generator=gen, dtype=torch.float32, device=model.rt.device)
-        x = 1.0 + norm_std * x if decl.init == "norm" else matrix_std * x
+        x = _shape_draw(x, decl.init, matrix_std, norm_std)
         tensors[name] = x if decl.keep_float32 else x.to(model.rt.dtype)
     model.bind(tensors, tied)
     return model
