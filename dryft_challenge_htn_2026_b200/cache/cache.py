@@ -188,6 +188,19 @@ class Cache:
         width = max([min_width] + [len(r) for r in rows])
         return [r + [-1] * (width - len(r)) for r in rows]
 
+    def state_snapshot(self, slots):
+        """Copies of the per-sequence states of ``slots`` (every state group), for a caller that runs a
+        step more than once (the warm-up runs before a graph capture) and must leave the states as one run
+        would: ``state_restore`` puts them back. Keys and values need none: a repeated step rewrites the
+        same cache rows with the same numbers."""
+        index = torch.tensor(list(slots), dtype=torch.long, device=self.groups[0].store.device) if self.groups else None
+        return [(g, index, g.store[:, index].clone()) for g in self.groups if isinstance(g, StateGroup) and g.store is not None]
+
+    @staticmethod
+    def state_restore(snapshot):
+        for g, index, saved in snapshot:
+            g.store[:, index] = saved
+
     def pages_held(self, slot):
         """Per key/value group the length of the slot's page list (pages given back included): it
         changes exactly when a step's page tables have to be written anew."""

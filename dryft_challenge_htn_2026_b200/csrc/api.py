@@ -697,6 +697,68 @@ def attention_masked(q, out, gate, out_scale, k_store, v_store, row_pos, row_seq
                                         _p(sink), _stream()), "attention_masked")
 
 
+MASKED_TILE_ROWS = 64            # queries a block of attention_masked_prefill_bf16 takes
+_MASKED_DECODE_SMEM = 200 * 1024
+
+
+def _masked_lib(head_dim, v_head_dim):
+    if head_dim % 16 or v_head_dim % 16 or not 16 <= head_dim <= 256 or not 16 <= v_head_dim <= 256:
+        raise KernelError(f"bfloat16 masked attention: head sizes {head_dim}/{v_head_dim} not supported (multiples of 16 up to 256)")
+    return _lib("attention_masked_bf16.cu", {"HD": head_dim, "HDV": v_head_dim})
+
+
+def masked_bf16_takes(head_dim, v_head_dim):
+    return head_dim % 16 == 0 and v_head_dim % 16 == 0 and 16 <= head_dim <= 256 and 16 <= v_head_dim <= 256
+
+
+def attention_masked_prefill_bf16(q, out, gate, out_scale, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads,
+                                  n_kv_heads, head_dim, v_head_dim, window, chunk, scale, r1=None, r2=None, sink=None):
+    """``attention_masked`` for ragged query portions on the tensor cores (bfloat16). tiles [n, 2] int32 =
+    (sequence, first query of a 64-row tile within its portion); cu_q [nseq+1]; seq_pos0 [nseq]."""
+    _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16), _need_rows(gate, "gate", torch.bfloat16)
+    _need(tiles, "tiles", torch.int32, 2), _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", torch.bfloat16), _need(v_store, "v_store", torch.bfloat16)
+    _need(r1, "r1", torch.float32, 1), _need(r2, "r2", torch.float32, 1), _need(sink, "sink", torch.float32, 1)
+    if n_heads % n_kv_heads or (r1 is None) != (r2 is None) or q.stride(0) % 2 or out.stride(0) % 2 or \
+            (gate is not None and gate.stride(0) % 2):
+        raise KernelError("attention_masked_prefill_bf16: head counts or row strides not supported")
+    lib = _masked_lib(head_dim, v_head_dim)
+    _check(lib, lib.dk_attn_masked_prefill_bf16(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), _p(gate),
+                                                c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
+                                                _p(k_store), _p(v_store), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
+                                                _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
+                                                int(chunk or 0), c_float(scale), _p(r1), _p(r2), _p(sink), _stream()),
+           "attention_masked_prefill_bf16")
+
+
+def masked_decode_span(n_heads, n_kv_heads, head_dim, window, chunk, table_pages):
+    """The most keys a row of a decode step can see (chunk, window, or what the page table can hold), or
+    None when the scores of a kv head's query heads over that many keys do not fit a block's shared memory."""
+    span = min([x for x in (chunk, window, table_pages * PAGE) if x])
+    g = n_heads // n_kv_heads
+    return span if 4 * g * (head_dim + span) <= _MASKED_DECODE_SMEM else None
+
+
+def attention_masked_decode_bf16(q, out, gate, out_scale, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads,
+                                 head_dim, v_head_dim, window, chunk, scale, span, r1=None, r2=None, sink=None):
+    """``attention_masked`` for one query token per sequence (bfloat16 storage, float32 arithmetic): a block
+    per (kv head, row) for all query heads of the group. ``span`` from ``masked_decode_span``."""
+    _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16), _need_rows(gate, "gate", torch.bfloat16)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
+    _need(k_store, "k_store", torch.bfloat16), _need(v_store, "v_store", torch.bfloat16)
+    _need(r1, "r1", torch.float32, 1), _need(r2, "r2", torch.float32, 1), _need(sink, "sink", torch.float32, 1)
+    if n_heads % n_kv_heads or (r1 is None) != (r2 is None) or q.stride(0) % 2 or out.stride(0) % 2 or \
+            (gate is not None and gate.stride(0) % 2):
+        raise KernelError("attention_masked_decode_bf16: head counts or row strides not supported")
+    lib = _masked_lib(head_dim, v_head_dim)
+    _check(lib, lib.dk_attn_masked_decode_bf16(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), _p(gate),
+                                               c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
+                                               _p(k_store), _p(v_store), _p(row_pos), _p(page_table), page_table.shape[1],
+                                               q.shape[0], n_heads, n_kv_heads, int(window or 0), int(chunk or 0),
+                                               c_float(scale), _p(r1), _p(r2), _p(sink), int(span), _stream()),
+           "attention_masked_decode_bf16")
+
+
 # ------------------------------------------------------------------------ decayed linear attention
 def linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim):
     """The recurrence S <- d_h S + silu(k) silu(v)^T, o = S^T silu(q), token by token, for the token rows
@@ -714,6 +776,39 @@ def linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, 
     _check(lib, lib.dk_linear_attention_step(_dt(q), _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out), _p(state),
                                              _p(cu_q), _p(seq_pos0), _p(seq_slot), _p(decay), n_seq, n_heads, head_dim,
                                              v_head_dim, _stream()), "linear_attention_step")
+
+
+CHUNK_MIN_TOKENS = 16     # portions at least this long go to the 64-token-block kernel
+
+
+def linear_attention(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim,
+                     max_len=None):
+    """The recurrence of ``linear_attention_step`` by the kernel that suits the step. ``max_len``: the most
+    tokens a sequence brings in this step, if the host knows it (None or 1: single tokens). bfloat16
+    portions of ``CHUNK_MIN_TOKENS`` tokens or more run in blocks of 64 tokens on the tensor cores (head sizes
+    in steps of 16, rows on 16-byte boundaries); everything else token by token."""
+    if q.dtype == torch.bfloat16 and cu_q is not None and max_len is not None and max_len >= CHUNK_MIN_TOKENS \
+            and head_dim % 16 == 0 and v_head_dim % 16 == 0 and q.stride(0) % 8 == 0 \
+            and all(t.data_ptr() % 16 == 0 for t in (q, k, v)):
+        return linear_attention_chunk_bf16(q, k, v, out, state, cu_q, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim)
+    return linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim)
+
+
+def linear_attention_chunk_bf16(q, k, v, out, state, cu_q, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim):
+    """``linear_attention_step`` for portions of many tokens in bfloat16: blocks of 64 tokens, the products
+    inside a block and with the state on the tensor cores, the state itself in float32."""
+    _need_rows(q, "q", torch.bfloat16), _need_rows(k, "k", torch.bfloat16), _need_rows(v, "v", torch.bfloat16)
+    _need(out, "out", torch.float32, 2), _need(state, "state", torch.float32, 4), _need(decay, "decay", torch.float32, 1)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.shape[1] != n_heads * head_dim or \
+            v.shape[1] != n_heads * v_head_dim or tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or \
+            decay.numel() != n_heads or head_dim % 16 or v_head_dim % 16 or not 16 <= head_dim <= 256 or \
+            q.stride(0) % 8 or any(t.data_ptr() % 16 for t in (q, k, v)):
+        raise KernelError("linear_attention_chunk_bf16: shapes not supported (head sizes in steps of 16, aligned rows)")
+    lib = _lib("linear_attention_bf16.cu", {"HD": head_dim})
+    _check(lib, lib.dk_linear_attention_chunk_bf16(_p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out), _p(state), _p(cu_q),
+                                                   _p(seq_slot), _p(decay), n_seq, n_heads, v_head_dim, _stream()),
+           "linear_attention_chunk_bf16")
 
 
 def norm_gate(o, weight, eps, gate, out_scale, out):

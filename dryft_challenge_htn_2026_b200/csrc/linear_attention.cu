@@ -5,14 +5,9 @@
 // sigmoid(gate), times a constant. State, decay powers, scores and sums are float32; the projections
 // come in the model's storage type and their activation is worked out in float32.
 //
-// Two forms of the recurrence:
-//   * linear_attention_step_kernel: token by token, one block per (sequence, head), the state in
-//     registers. Serves single-token steps and any float32 step.
-//   * linear_attention_chunk_kernel (bfloat16 storage): a portion of a sequence in blocks of 64 tokens:
-//     inside a block o = ((Q K^T) * D) V with D_ij = d^(i-j) for j <= i, across blocks through the
-//     state, o += d^(i+1) Q S and S <- d^64 S + (K * d^(63-j))^T V; the three products of a block on
-//     tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums), the state split in a high and a
-//     low bfloat16 half so that it enters its product with 16 bits of mantissa.
+// This file: the recurrence token by token, one block per (sequence, head), the state in registers; it
+// serves single-token steps, short portions and every float32 step. Portions of many tokens in bfloat16
+// run in blocks of 64 tokens on the tensor cores (linear_attention_bf16.cu).
 #include "common.cuh"
 
 #define LA_THREADS 256

@@ -212,13 +212,17 @@ class DecodeState:
 
     def capture(self):
         """Two plain runs that leave positions and tokens alone (they compile and size everything,
-        and only rewrite cache rows the real step writes again), then the captured one."""
+        and only rewrite cache rows the real step writes again), then the captured one. Per-sequence
+        states (mixers with a recurrence) are not idempotent under a repeated step: they are saved
+        before the plain runs and put back after them."""
         scratch_tok = torch.empty_like(self.ctx.tok)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
+            saved = self.runner.cache.state_snapshot([slot for slot, _ in self.filled or []])
             for _ in range(2):
                 self.body(advance=False, out_tok=scratch_tok)
+            self.runner.cache.state_restore(saved)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()

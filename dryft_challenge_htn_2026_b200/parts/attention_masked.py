@@ -12,6 +12,7 @@ import torch
 from ..cache.requests import KVRequest
 from ..config.specs import MaskedAttentionSpec
 from ..csrc import api
+from .attention import QueryTiles
 from .base import ParamDecl, Part, register_part
 from .linear import linear
 
@@ -33,6 +34,13 @@ class MaskedAttention(Part):
             raise ValueError("bfloat16 projections need inner sizes that are multiples of 8, not "
                              f"{s.hidden_size} / {self.n_mid}")
         self.r1 = self.r2 = self.sink = None
+        # the tensor-core kernels take bfloat16 with head sizes in steps of 16; everything else (float32, odd
+        # head sizes) runs on the float32-arithmetic kernel, which serves every phase
+        self.tensor_core = rt.dtype == torch.bfloat16 and api.masked_bf16_takes(s.head_dim, s.v_head_dim)
+        self.tiles = QueryTiles(api.MASKED_TILE_ROWS) if self.tensor_core else None
+
+    def step_plans(self):
+        return [self.tiles] if self.tiles is not None else []
 
     def param_decls(self):
         s = self.spec
@@ -77,8 +85,16 @@ class MaskedAttention(Part):
         gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
         if writes:
             api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
-        api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_heads,
-                             s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale, self.r1, self.r2,
+        sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
+        if self.tensor_core and not ctx.is_decode:
+            return api.attention_masked_prefill_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tiles.key], ctx.cu_q,
+                                                     ctx.seq_pos0, table, *sizes, self.r1, self.r2, self.sink)
+        if self.tensor_core:
+            span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1])
+            if span is not None:
+                return api.attention_masked_decode_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, table, *sizes, span,
+                                                        self.r1, self.r2, self.sink)
+        api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, *sizes, self.r1, self.r2,
                              self.sink)
 
     def forward(self, ctx, views, a, writes=True):

@@ -68,11 +68,11 @@ class LinearAttention(Part):
         gate = proj[:, 2 * self.n_qk + self.n_mid:] if s.output_gate else None
         o = torch.empty((ctx.n_tok, self.n_mid), dtype=torch.float32, device=self.rt.device)
         if ctx.is_decode:      # one token a row; padding rows carry position -1
-            api.linear_attention_step(q, k, v, o, state, None, ctx.row_pos, ctx.seq_slot, self.decay, ctx.n_tok,
-                                      s.num_heads, s.head_dim, s.v_head_dim)
+            api.linear_attention(q, k, v, o, state, None, ctx.row_pos, ctx.seq_slot, self.decay, ctx.n_tok,
+                                 s.num_heads, s.head_dim, s.v_head_dim, 1)
         else:
-            api.linear_attention_step(q, k, v, o, state, ctx.cu_q, ctx.seq_pos0, ctx.seq_slot, self.decay, ctx.n_seq,
-                                      s.num_heads, s.head_dim, s.v_head_dim)
+            api.linear_attention(q, k, v, o, state, ctx.cu_q, ctx.seq_pos0, ctx.seq_slot, self.decay, ctx.n_seq,
+                                 s.num_heads, s.head_dim, s.v_head_dim, int(ctx.host["lens"].max()))
         if self.norm_weight is None:
             raise ValueError("linear attention without an output norm is not implemented")
         api.norm_gate(o, self.norm_weight, s.out_norm.eps, gate, scale, mid)

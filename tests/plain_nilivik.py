@@ -73,6 +73,37 @@ def chunk_mask(T, chunk):
     return (j <= i) & (i // chunk == j // chunk)
 
 
+def attention_core(q, k, v, scale, chunk=None, r1=None, r2=None, sink=None, window=None, first_position=0):
+    """q [T, H, D], k [T, G, D], v [T, G, Dv] of one whole sequence -> heads [T, H, Dv]. Every option
+    is written out separately: mask (causal, chunk, window), distance bias, sink."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    pos = torch.arange(first_position, first_position + T)
+    i, j = pos[:, None], pos[None, :]
+    see = j <= i
+    if chunk is not None:
+        see = see & (i // chunk == j // chunk)
+    if window is not None:
+        see = see & (j > i - window)
+    dist = (i - j).clamp(min=0).to(q.dtype)
+    heads = []
+    for h in range(H):
+        g = h // (H // G)
+        s = (q[:, h] @ k[:, g].T) * scale
+        if r1 is not None:
+            s = s - r1[h] * torch.log1p(r2[h] * dist)
+        s = s.masked_fill(~see, -math.inf)
+        top = s.max(-1, keepdim=True).values
+        if sink is not None:
+            top = torch.maximum(top, sink[h])
+        e = torch.exp(s - top)
+        den = e.sum(-1, keepdim=True)
+        if sink is not None:
+            den = den + torch.exp(sink[h] - top)
+        heads.append((e / den) @ v[:, g])
+    return torch.stack(heads, 1)
+
+
 def left_attention(a, w, m):
     """``w``: the left mixer's tensors by short name; ``m``: its config. Returns [T, W]."""
     T = a.shape[0]
@@ -80,35 +111,34 @@ def left_attention(a, w, m):
     q = (a @ w["q"].T).view(T, H, D)
     k = (a @ w["k"].T).view(T, G, D)
     v = (a @ w["v"].T).view(T, G, Dv)
-    dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).clamp(min=0).to(a.dtype)
-    see = chunk_mask(T, m["mask"]["size"])
-    heads = []
-    for h in range(H):
-        g = h // (H // G)
-        s = (q[:, h] @ k[:, g].T) * m["scale"] - w["r1"][h] * torch.log1p(w["r2"][h] * dist)
-        s = s.masked_fill(~see, -math.inf)
-        top = torch.maximum(s.max(-1, keepdim=True).values, w["sink"][h])
-        e = torch.exp(s - top)
-        p = e / (e.sum(-1, keepdim=True) + torch.exp(w["sink"][h] - top))
-        heads.append(p @ v[:, g])
-    o = torch.cat(heads, -1) * torch.sigmoid(a @ w["g"].T)
+    chunk = m["mask"]["size"] if m.get("mask") else None
+    heads = attention_core(q, k, v, m["scale"], chunk, w["r1"], w["r2"], w["sink"])
+    o = heads.reshape(T, H * Dv) * torch.sigmoid(a @ w["g"].T)
     return o @ w["o"].T
 
 
+def decay_recurrence(q, k, v, decay, state=None):
+    """q, k [T, H, D], v [T, H, Dv] -> (o [T, H, Dv], last state [H, D, Dv]); token by token, exactly
+    as the recurrence is written."""
+    T, H, D = q.shape
+    Dv = v.shape[2]
+    S = torch.zeros(H, D, Dv, dtype=q.dtype) if state is None else state.clone()
+    out = torch.zeros(T, H, Dv, dtype=q.dtype)
+    for t in range(T):
+        for h in range(H):
+            S[h] = decay[h] * S[h] + torch.outer(k[t, h], v[t, h])
+            out[t, h] = S[h].T @ q[t, h]
+    return out, S
+
+
 def right_recurrence(a, w, m, eps):
-    """Token by token, exactly as the recurrence is written."""
     T = a.shape[0]
     H, D, Dv = m["heads"], m["dim"], m["vdim"]
     decay = m["decay"] if isinstance(m["decay"], (list, tuple)) else [m["decay"]] * H
     q = F.silu(a @ w["q"].T).view(T, H, D)
     k = F.silu(a @ w["k"].T).view(T, H, D)
     v = F.silu(a @ w["v"].T).view(T, H, Dv)
-    S = torch.zeros(H, D, Dv, dtype=a.dtype)
-    out = torch.zeros(T, H, Dv, dtype=a.dtype)
-    for t in range(T):
-        for h in range(H):
-            S[h] = decay[h] * S[h] + torch.outer(k[t, h], v[t, h])
-            out[t, h] = S[h].T @ q[t, h]
+    out, _ = decay_recurrence(q, k, v, decay)
     o = weighted_norm(out.reshape(T, H * Dv), w["norm"], eps) * torch.sigmoid(a @ w["g"].T)
     return o @ w["o"].T
 
