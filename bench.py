@@ -302,6 +302,230 @@ def run_ours(args):
     return 0
 
 
+# --------------------------------------------------------------- another design beside Qwen3 at equal size
+def nilivik_config(width, heads, kv_heads, ff_qwen, layers, vocab, chunk):
+    """A Nilivik model of Qwen3's width, head size 128 and layer count, with as many parameters a layer:
+    chunked attention of Qwen3's head counts, linear attention of half as many heads, and a feed-forward
+    sized so that the layer's matrices add up to Qwen3's."""
+    hd, rh = 128, heads // 2
+    qwen = (heads + 2 * kv_heads) * hd + heads * hd + 3 * ff_qwen            # matrix columns of a Qwen3 layer, per width
+    mix = (2 * heads + 2 * kv_heads) * hd + heads * hd + 4 * rh * hd + rh * hd
+    ff = max(256, (qwen - mix) // 2 // 64 * 64)
+    layer = {"type": "parallel",
+             "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": hd, "vdim": hd, "mask": {"size": chunk},
+                                "scale": hd ** -0.5},
+                       "right": {"heads": rh, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(3 + 5 * i / max(1, rh - 1)) for i in range(rh)]},
+                       "left_scale": 0.7, "right_scale": 0.7},
+             "mlp": {"kind": "dense", "ff": ff}}
+    return dict(architecture="Nilivik", vocab=vocab, width=width, embedding={"scale": 1.0}, norm={"eps": 1e-6},
+                logit_softcap=30.0, layers=[layer] * layers)
+
+
+def time_step_prefill(torch, dk, model, tokens, iters=3):
+    import numpy as np
+    runner = dk.Runner(model, tokens + 64, max_slots=2)
+    prompt = np.random.RandomState(7).randint(0, model.spec.vocab_size, tokens).tolist()
+    times = []
+    for i in range(iters + 2):
+        slot = runner.begin()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([(slot, prompt, [tokens - 1])], graph=True)
+        e1.record()
+        torch.cuda.synchronize()
+        runner.end(slot)
+        if i >= 2:
+            times.append(e0.elapsed_time(e1))
+    del runner
+    torch.cuda.empty_cache()
+    return statistics.median(times)
+
+
+def time_step_decode(torch, dk, model, batch, context, steps, warmup):
+    """Decode steps of the generation loop's decode state (graph replay) for ``batch`` sequences that hold
+    ``context`` tokens each; returns (ms a step, kernels a step)."""
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
+    from dryft_challenge_htn_2026_b200.sampling import SamplingParams
+    total_new = warmup + steps + 8
+    runner = dk.Runner(model, batch * ((context + total_new + 63) // 64 * 64), max_slots=batch)
+    backend = GpuBackend(runner, use_graph=True)
+    prompts = random_prompts(model.spec.vocab_size, [context] * batch, 3)
+    backend.start(prompts, SamplingParams(total_new), [0] * batch).wait()
+    st = backend.state
+    saved = runner.cache.state_snapshot([slot for slot, _ in st.filled])
+    count0 = api.launch_count()
+    st.body(advance=False, out_tok=torch.empty_like(st.ctx.tok))
+    launches = api.launch_count() - count0
+    runner.cache.state_restore(saved)
+    st.capture()
+    for _ in range(warmup):
+        st.run()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(steps):
+        st.run()
+    ev[1].record()
+    torch.cuda.synchronize()
+    ms = ev[0].elapsed_time(ev[1]) / steps
+    backend.finish()
+    del st, backend, runner
+    torch.cuda.empty_cache()
+    return ms, launches
+
+
+def kernel_times(torch, dk, pk, heads, kv_heads, rh, chunk):
+    """The new design's mixer kernels alone, beside the attention kernels of Qwen3 at the same head counts:
+    CUDA events around one launch, L2 flushed before each (a 256 MB write), median of 5 after 2 untimed."""
+    from dryft_challenge_htn_2026_b200.cache import Cache, KVRequest, StateRequest
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.engine.batch import build_context
+    from dryft_challenge_htn_2026_b200.parts.attention import QueryTiles
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    hd = 128
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for i in range(7):
+            flush.fill_(float(i))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[2:]) * 1e3        # microseconds
+
+    out = {}
+    r1 = torch.full((heads,), 0.3, device=dev)
+    r2 = torch.full((heads,), 0.1, device=dev)
+    sink = torch.zeros(heads, device=dev)
+    decay = torch.tensor([1.0 - 2.0 ** -(3 + 5 * i / max(1, rh - 1)) for i in range(rh)], dtype=torch.float32, device=dev)
+    for tokens in (2048, 8192):
+        # ---- prompts: masked attention (this design) and Qwen3's attention, one sequence of ``tokens``
+        plans = [QueryTiles(api.MASKED_TILE_ROWS), QueryTiles(api.TC_TILE_ROWS)]
+        cache = Cache([[KVRequest(kv_heads, hd, None, bf, hd, chunk)], [KVRequest(kv_heads, hd, None, bf)],
+                       [StateRequest((rh, hd, hd), torch.float32)]], tokens + 64, 2, dev)
+        slot = cache.begin()
+        ctx = build_context(cache, [(slot, [0] * tokens, [])], dev, plans=plans)
+        q = torch.randn(tokens, heads * hd, device=dev).to(bf)
+        g = torch.randn(tokens, heads * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        for e in (0, 1):
+            v = cache.views(e)[0]
+            v.k.normal_(), v.v.normal_()
+        m, f, stt = cache.views(0)[0], cache.views(1)[0], cache.views(2)[0].state
+        seen = sum(min(i % chunk, i) + 1 for i in range(tokens))
+        us = timed(lambda: api.attention_masked_prefill_bf16(q, o, g, 0.7, m.k, m.v, ctx.plans[plans[0].key], ctx.cu_q, ctx.seq_pos0,
+                                                             ctx.tables[m.group], heads, kv_heads, hd, hd, None, chunk, hd ** -0.5, r1, r2, sink))
+        out[f"masked_attention_prefill_{tokens}"] = {"us": round(us, 1), "tflops": round(4 * heads * hd * seen / us / 1e6, 1),
+                                                     "frac_bf16": round(4 * heads * hd * seen / us / 1e6 / pk["bf16_tflops"], 4)}
+        full = tokens * (tokens + 1) // 2
+        us = timed(lambda: api.attention_prefill_tc(q, o, f.k, f.v, ctx.plans[plans[1].key], ctx.cu_q, ctx.seq_pos0, ctx.tables[f.group],
+                                                    heads, kv_heads, hd, None, hd ** -0.5))
+        out[f"qwen3_attention_prefill_{tokens}"] = {"us": round(us, 1), "tflops": round(4 * heads * hd * full / us / 1e6, 1),
+                                                    "frac_bf16": round(4 * heads * hd * full / us / 1e6 / pk["bf16_tflops"], 4)}
+        # ---- prompts: linear attention in blocks of 64 tokens; what it must move: q, k, v in, float32 o out
+        x = torch.randn(tokens, 3 * rh * hd, device=dev).to(bf)
+        lo = torch.empty(tokens, rh * hd, dtype=torch.float32, device=dev)
+        us = timed(lambda: api.linear_attention(x[:, :rh * hd], x[:, rh * hd:2 * rh * hd], x[:, 2 * rh * hd:], lo, stt, ctx.cu_q, ctx.seq_pos0,
+                                                ctx.seq_slot, decay, 1, rh, hd, hd, tokens))
+        moved = tokens * rh * hd * (3 * 2 + 4)
+        flops = tokens * rh * (2 * 64 * 2 * hd + 4 * hd * hd)
+        out[f"linear_attention_prefill_{tokens}"] = {"us": round(us, 1), "gbs": round(moved / us / 1e3, 1),
+                                                     "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4),
+                                                     "tflops": round(flops / us / 1e6, 2)}
+        cache.end(slot)
+        del cache, q, g, o, x, lo
+    for batch in (8, 64):
+        # ---- single tokens: every sequence holds 3,000 tokens (952 of them in the newest chunk of 2,048)
+        context = 3000
+        cache = Cache([[KVRequest(kv_heads, hd, None, bf, hd, chunk)], [KVRequest(kv_heads, hd, None, bf)],
+                       [StateRequest((rh, hd, hd), torch.float32)]], batch * (context + 64), batch, dev)
+        slots = [cache.begin() for _ in range(batch)]
+        for sl in slots:
+            cache.reserve(sl, context)
+            cache.length[sl] = context
+        ctx = build_context(cache, [(sl, [0], []) for sl in slots], dev)
+        for e in (0, 1):
+            v = cache.views(e)[0]
+            v.k.normal_(), v.v.normal_()
+        m, f, stt = cache.views(0)[0], cache.views(1)[0], cache.views(2)[0].state
+        q = torch.randn(batch, heads * hd, device=dev).to(bf)
+        g = torch.randn(batch, heads * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        keys = context - context // chunk * chunk + 1
+        table = ctx.tables[m.group]
+        span = api.masked_decode_span(heads, kv_heads, hd, None, chunk, table.shape[1])
+        us = timed(lambda: api.attention_masked_decode_bf16(q, o, g, 0.7, m.k, m.v, ctx.row_pos, table, heads, kv_heads, hd, hd, None,
+                                                            chunk, hd ** -0.5, span, r1, r2, sink))
+        moved = batch * kv_heads * keys * 2 * hd * 2
+        out[f"masked_attention_decode_b{batch}"] = {"us": round(us, 1), "keys": keys, "gbs": round(moved / us / 1e3, 1),
+                                                    "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+        nsplit = api.decode_splits(batch, kv_heads, heads // kv_heads, ctx.tables[f.group].shape[1])
+        ws = api.attention_decode_ws(batch, heads, hd, nsplit, dev)
+        us = timed(lambda: api.attention_decode_bf16(q, o, f.k, f.v, ctx.row_pos, ctx.tables[f.group], heads, kv_heads, hd, None,
+                                                     hd ** -0.5, nsplit, *ws))
+        moved = batch * kv_heads * (context + 1) * 2 * hd * 2
+        out[f"qwen3_attention_decode_b{batch}"] = {"us": round(us, 1), "keys": context + 1, "gbs": round(moved / us / 1e3, 1),
+                                                   "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+        x = torch.randn(batch, 3 * rh * hd, device=dev).to(bf)
+        lo = torch.empty(batch, rh * hd, dtype=torch.float32, device=dev)
+        us = timed(lambda: api.linear_attention(x[:, :rh * hd], x[:, rh * hd:2 * rh * hd], x[:, 2 * rh * hd:], lo, stt, None, ctx.row_pos,
+                                                ctx.seq_slot, decay, batch, rh, hd, hd, 1))
+        moved = batch * rh * hd * hd * 4 * 2
+        out[f"linear_attention_decode_b{batch}"] = {"us": round(us, 1), "gbs": round(moved / us / 1e3, 1),
+                                                    "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+        del cache, q, g, o, x, lo
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_design(args):
+    """``--design nilivik``: prefill and decode of the Nilivik decoder at Qwen3 layer sizes (random weights,
+    ``--layers`` layers, default 4) beside Qwen3 itself at the same width, layer count and parameters a
+    layer, and the design's mixer kernels alone beside Qwen3's attention kernels. One JSON line."""
+    import torch
+
+    import dryft_challenge_htn_2026_b200 as dk
+    from dryft_challenge_htn_2026_b200.csrc import api
+
+    api.set_pdl(bool(args.pdl))
+    pk = peaks()
+    layers = args.layers or 4
+    chunk = 2048
+    vocab = 32768
+    out = {"design": args.design, "beside": "Qwen3ForCausalLM", "layers": layers, "chunk": chunk, "vocab": vocab, "dtype": "bf16",
+           "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
+    for size in args.design_sizes.split(","):
+        q = dict(SIZES[size]["config"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True)
+        n = nilivik_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers,
+                           vocab, chunk)
+        rec = {"width": q["hidden_size"], "nilivik_ff": n["layers"][0]["mlp"]["ff"]}
+        for name, cfg_d in (("nilivik", n), ("qwen3", q)):
+            model = dk.random_model(dk.config_from_dict(cfg_d), seed=0, dtype=torch.bfloat16)
+            r = {"weight_mb_per_step": round(model.weight_bytes_per_step() / 1e6, 1), "prefill": {}, "decode": {}}
+            for tokens in (2048, 8192):
+                ms = time_step_prefill(torch, dk, model, tokens)
+                r["prefill"][str(tokens)] = {"ms": round(ms, 3), "tok_s": round(tokens / ms * 1e3)}
+            for batch in (1, 8, 64):
+                ms, launches = time_step_decode(torch, dk, model, batch, 2048, max(16, args.steps // 2), 24)
+                r["decode"][f"b{batch}"] = {"ms": round(ms, 4), "tok_s": round(batch / ms * 1e3, 1), "kernels_per_step": launches,
+                                            "weights_frac_hbm": round(model.weight_bytes_per_step() / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            rec[name] = r
+            del model
+            torch.cuda.empty_cache()
+        rec["kernels"] = kernel_times(torch, dk, pk, q["num_attention_heads"], q["num_key_value_heads"],
+                                      q["num_attention_heads"] // 2, chunk)
+        out["sizes"][size] = rec
+    api.gemm_tc_check()
+    print(json.dumps(out))
+    return 0
+
+
 # ------------------------------------------------------------------------------ the reference arm
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 # The reference's own switches (engine/engine.py:31,98; engine/fused.py:19), set in the environment before it
@@ -501,12 +725,18 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --prefill-only: a prompt of another length")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
+    ap.add_argument("--design", default=None, choices=["nilivik"],
+                    help="instead of the default workload: prefill and decode of this design at Qwen3 layer sizes beside Qwen3 "
+                         "itself at equal size, and its mixer kernels alone (one JSON line of its own)")
+    ap.add_argument("--design-sizes", default="4b,8b", help="with --design: which of the layer sizes")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs one model on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.design:
+        return run_design(args)
     return run_ours(args)
 
 

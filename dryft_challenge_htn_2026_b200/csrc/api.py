@@ -698,7 +698,7 @@ def attention_masked(q, out, gate, out_scale, k_store, v_store, row_pos, row_seq
 
 
 MASKED_TILE_ROWS = 64            # queries a block of attention_masked_prefill_bf16 takes
-_MASKED_DECODE_SMEM = 200 * 1024
+_MASKED_DECODE_SMEM = 224 * 1024 - 32 * 1024      # a block's shared memory less the 32 KB where partial sums meet
 
 
 def _masked_lib(head_dim, v_head_dim):
@@ -786,9 +786,9 @@ def linear_attention(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq
     """The recurrence of ``linear_attention_step`` by the kernel that suits the step. ``max_len``: the most
     tokens a sequence brings in this step, if the host knows it (None or 1: single tokens). bfloat16
     portions of ``CHUNK_MIN_TOKENS`` tokens or more run in blocks of 64 tokens on the tensor cores (head sizes
-    in steps of 16, rows on 16-byte boundaries); everything else token by token."""
+    in steps of 16, keys up to 128, rows on 16-byte boundaries); everything else token by token."""
     if q.dtype == torch.bfloat16 and cu_q is not None and max_len is not None and max_len >= CHUNK_MIN_TOKENS \
-            and head_dim % 16 == 0 and v_head_dim % 16 == 0 and q.stride(0) % 8 == 0 \
+            and head_dim % 16 == 0 and head_dim <= 128 and v_head_dim % 16 == 0 and q.stride(0) % 8 == 0 \
             and all(t.data_ptr() % 16 == 0 for t in (q, k, v)):
         return linear_attention_chunk_bf16(q, k, v, out, state, cu_q, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim)
     return linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim)
@@ -796,19 +796,20 @@ def linear_attention(q, k, v, out, state, cu_q, seq_pos0, seq_slot, decay, n_seq
 
 def linear_attention_chunk_bf16(q, k, v, out, state, cu_q, seq_slot, decay, n_seq, n_heads, head_dim, v_head_dim):
     """``linear_attention_step`` for portions of many tokens in bfloat16: blocks of 64 tokens, the products
-    inside a block and with the state on the tensor cores, the state itself in float32."""
+    inside a block and with the state on the tensor cores, the state itself in float32. q, k and v are
+    overwritten by their activation."""
     _need_rows(q, "q", torch.bfloat16), _need_rows(k, "k", torch.bfloat16), _need_rows(v, "v", torch.bfloat16)
     _need(out, "out", torch.float32, 2), _need(state, "state", torch.float32, 4), _need(decay, "decay", torch.float32, 1)
     _need(cu_q, "cu_q", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.shape[1] != n_heads * head_dim or \
             v.shape[1] != n_heads * v_head_dim or tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or \
-            decay.numel() != n_heads or head_dim % 16 or v_head_dim % 16 or not 16 <= head_dim <= 256 or \
+            decay.numel() != n_heads or head_dim % 16 or v_head_dim % 16 or not 16 <= head_dim <= 128 or \
             q.stride(0) % 8 or any(t.data_ptr() % 16 for t in (q, k, v)):
-        raise KernelError("linear_attention_chunk_bf16: shapes not supported (head sizes in steps of 16, aligned rows)")
+        raise KernelError("linear_attention_chunk_bf16: shapes not supported (head sizes in steps of 16, keys up to 128, aligned rows)")
     lib = _lib("linear_attention_bf16.cu", {"HD": head_dim})
-    _check(lib, lib.dk_linear_attention_chunk_bf16(_p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out), _p(state), _p(cu_q),
-                                                   _p(seq_slot), _p(decay), n_seq, n_heads, v_head_dim, _stream()),
-           "linear_attention_chunk_bf16")
+    _check(lib, lib.dk_linear_attention_chunk_bf16(_p(q), _p(k), _p(v), c_longlong(q.stride(0)), c_longlong(q.shape[0]), _p(out),
+                                                   _p(state), _p(cu_q), _p(seq_slot), _p(decay), n_seq, n_heads, v_head_dim,
+                                                   _stream()), "linear_attention_chunk_bf16", 2)
 
 
 def norm_gate(o, weight, eps, gate, out_scale, out):

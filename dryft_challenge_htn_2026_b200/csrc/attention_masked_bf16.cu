@@ -11,8 +11,9 @@
 //    the unrounded values. The sink joins the denominator after the last page; the gate and the constant
 //    factor are applied to the float32 result before it is stored.
 //  * decode: one query token per sequence; a block owns the query heads that share a kv head: scores of
-//    all visible keys into shared memory (a lane per key), softmax with the sink over them, then P.V with a
-//    thread per output column. A chunk or window bounds the keys, so there is no split over blocks.
+//    all visible keys into shared memory (a thread per key), softmax with the sink over them, then P.V with
+//    eight output columns and every 16th (or so) key a thread, the partial sums meeting in shared memory. A
+//    chunk or window bounds the keys, so there is no split over blocks.
 #include "attention_mma.cuh"
 
 #ifndef HDV
@@ -224,9 +225,13 @@ attn_masked_prefill_kernel(const bf16* q, long long ldq, bf16* out, long long ld
 }
 
 // -------------------------------------------------------------------------------------- decode
-// grid (nkv, rows). Block: the G query heads of one kv head for one row (sequence); 128 threads.
-// Shared memory: q [G][HD] float, scores [G][span] float with span = the most keys a row can see.
-__global__ void __launch_bounds__(128)
+// grid (nkv, rows). Block: the G query heads of one kv head for one row (sequence); 256 threads.
+// Shared memory: q [G][HD] float, scores [G][span] float with span = the most keys a row can see, and
+// 32 KB in which the threads' partial sums of P.V meet.
+constexpr int MD_THREADS = 256;
+constexpr int MD_RED_FLOATS = MD_THREADS * 4 * 8;
+
+__global__ void __launch_bounds__(MD_THREADS)
 attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo, const bf16* gate, long long ldg,
                           float out_scale, const bf16* k_store, const bf16* v_store, const int* row_pos,
                           const int* page_table, int pt_stride, int nh, int nkv, int window, int chunk, float scale,
@@ -234,27 +239,29 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
                           int span) {
     extern __shared__ __align__(16) float fsm[];
     const int G = nh / nkv, kvh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
-    float* qs = fsm;                 // [G][HD]
-    float* sc = fsm + G * HD;        // [G][span]
+    float* red = fsm;                       // [key split][4 heads][HDV]
+    float* qs = fsm + MD_RED_FLOATS;        // [G][HD]
+    float* sc = qs + G * HD;                // [G][span]
     pdl_wait();
     pdl_launch_dependents();
     const int pos = row_pos[b];
     if (pos < 0) {
-        for (int i = tid; i < G * HDV; i += blockDim.x) out[(size_t)b * ldo + (size_t)kvh * G * HDV + i] = __float2bfloat16_rn(0.f);
+        for (int i = tid; i < G * HDV; i += MD_THREADS) out[(size_t)b * ldo + (size_t)kvh * G * HDV + i] = __float2bfloat16_rn(0.f);
         return;
     }
     const int lo = first_key(pos, window, chunk), n = pos - lo + 1;
     const int* pt = page_table + (size_t)b * pt_stride;
-    for (int i = tid; i < G * HD; i += blockDim.x) qs[i] = __bfloat162float(q[(size_t)b * ldq + (size_t)kvh * G * HD + i]);
+    for (int i = tid; i < G * HD; i += MD_THREADS) qs[i] = __bfloat162float(q[(size_t)b * ldq + (size_t)kvh * G * HD + i]);
     __syncthreads();
-    // scores: a thread per key, the key row read in 16-byte pieces, all G heads from one read
-    for (int jj = tid; jj < n; jj += blockDim.x) {
+    // scores: a thread per key, the key row read in 16-byte pieces, four heads from one read
+    for (int jj = tid; jj < n; jj += MD_THREADS) {
         const int j = lo + jj;
         const bf16* kr = k_store + kv_offset(pt[j / DK_PAGE], nkv, kvh, j % DK_PAGE, HD);
         float dot[4];
-        for (int g0 = 0; g0 < G; g0 += 4) {       // four heads a pass over the key row (later passes hit the L1)
+        for (int g0 = 0; g0 < G; g0 += 4) {       // later passes over the key row hit the L1
             const int gn = min(4, G - g0);
             dot[0] = dot[1] = dot[2] = dot[3] = 0.f;
+#pragma unroll 4
             for (int c = 0; c < HD; c += 8) {
                 const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
                 const bf16* kv8 = reinterpret_cast<const bf16*>(&raw);
@@ -277,9 +284,9 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
         }
     }
     __syncthreads();
-    // softmax with the sink, head by head: a warp per head at a time
+    // softmax with the sink, head by head: a warp per head at a time; the weights leave normalised
     const int lane = tid & 31, warp = tid >> 5;
-    for (int gq = warp; gq < G; gq += 4) {
+    for (int gq = warp; gq < G; gq += MD_THREADS / 32) {
         const int h = kvh * G + gq;
         float mx = sink ? sink[h] : -INFINITY;
         for (int jj = lane; jj < n; jj += 32) mx = fmaxf(mx, sc[gq * span + jj]);
@@ -296,25 +303,50 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
         for (int jj = lane; jj < n; jj += 32) sc[gq * span + jj] *= inv;
     }
     __syncthreads();
-    // P.V: a thread per (head, pair of output columns); the value rows are read side by side by the threads
-    for (int i = tid; i < G * (HDV / 2); i += blockDim.x) {
-        const int gq = i / (HDV / 2), d = (i % (HDV / 2)) * 2;
-        float a0 = 0.f, a1 = 0.f;
-        for (int jj = 0; jj < n; jj++) {
-            const int j = lo + jj;
-            const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(
-                v_store + kv_offset(pt[j / DK_PAGE], nkv, kvh, j % DK_PAGE, HDV) + d);
-            const float p = sc[gq * span + jj];
-            a0 = fmaf(p, __bfloat162float(vv.x), a0);
-            a1 = fmaf(p, __bfloat162float(vv.y), a1);
+    // P.V: a thread takes 8 output columns and every KS-th key, for four heads at a time from one read of the value
+    // row; the KS partial sums of a column meet in shared memory
+    constexpr int CGN = HDV / 8, KS = MD_THREADS / CGN;
+    const int cgp = tid % CGN, ks = tid / CGN;
+    for (int g0 = 0; g0 < G; g0 += 4) {
+        const int gn = min(4, G - g0);
+        float acc[4][8];
+#pragma unroll
+        for (int gg = 0; gg < 4; gg++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[gg][e] = 0.f;
+        if (ks < KS) {
+#pragma unroll 4
+            for (int jj = ks; jj < n; jj += KS) {
+                const int j = lo + jj;
+                const uint4 raw = *reinterpret_cast<const uint4*>(
+                    v_store + kv_offset(pt[j / DK_PAGE], nkv, kvh, j % DK_PAGE, HDV) + cgp * 8);
+                const bf16* v8 = reinterpret_cast<const bf16*>(&raw);
+                float vf[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) vf[e] = __bfloat162float(v8[e]);
+#pragma unroll
+                for (int gg = 0; gg < 4; gg++)
+                    if (gg < gn) {
+                        const float p = sc[(g0 + gg) * span + jj];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) acc[gg][e] = fmaf(p, vf[e], acc[gg][e]);
+                    }
+            }
+#pragma unroll
+            for (int gg = 0; gg < 4; gg++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) red[(ks * 4 + gg) * HDV + cgp * 8 + e] = acc[gg][e];
         }
-        const size_t col = (size_t)(kvh * G + gq) * HDV + d;
-        if (gate) {
-            const __nv_bfloat162 gg = *reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)b * ldg + col);
-            a0 *= 1.f / (1.f + expf(-__bfloat162float(gg.x)));
-            a1 *= 1.f / (1.f + expf(-__bfloat162float(gg.y)));
+        __syncthreads();
+        for (int i = tid; i < gn * HDV; i += MD_THREADS) {
+            const int gg = i / HDV, d = i % HDV;
+            float a = 0.f;
+            for (int kk = 0; kk < KS; kk++) a += red[(kk * 4 + gg) * HDV + d];
+            const size_t col = (size_t)(kvh * G + g0 + gg) * HDV + d;
+            if (gate) a *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)b * ldg + col])));
+            out[(size_t)b * ldo + col] = __float2bfloat16_rn(a);
         }
-        *reinterpret_cast<uint32_t*>(out + (size_t)b * ldo + col) = pack_bf16(a0, a1);
+        __syncthreads();
     }
 }
 
@@ -344,14 +376,14 @@ DK_EXPORT int dk_attn_masked_decode_bf16(const void* q, long long ldq, void* out
                                          const float* sink, int span, cudaStream_t st) {
     if (nh % nkv != 0) return (int)cudaErrorInvalidValue;
     const int G = nh / nkv;
-    const size_t smem = sizeof(float) * ((size_t)G * HD + (size_t)G * span);
-    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    const size_t smem = sizeof(float) * ((size_t)MD_RED_FLOATS + (size_t)G * HD + (size_t)G * span);
+    if (smem > 224 * 1024) return (int)cudaErrorInvalidValue;
     static size_t attr = 48 * 1024;
     if (smem > attr) {
         cudaFuncSetAttribute(attn_masked_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr = smem;
     }
-    return dk_launch(attn_masked_decode_kernel, dim3(nkv, n_rows), dim3(128), smem, st, (const bf16*)q, ldq, (bf16*)out,
+    return dk_launch(attn_masked_decode_kernel, dim3(nkv, n_rows), dim3(MD_THREADS), smem, st, (const bf16*)q, ldq, (bf16*)out,
                      ldo, (const bf16*)gate, ldg, out_scale, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table,
                      pt_stride, nh, nkv, window, chunk, scale, r1, r2, sink, span);
 }
