@@ -421,6 +421,10 @@ def kernel_times(torch, dk, pk, heads, kv_heads, rh, chunk):
         seen = sum(min(i % chunk, i) + 1 for i in range(tokens))
         us = timed(lambda: api.attention_masked_prefill_bf16(q, o, g, 0.7, m.k, m.v, ctx.plans[plans[0].key], ctx.cu_q, ctx.seq_pos0,
                                                              ctx.tables[m.group], heads, kv_heads, hd, hd, None, chunk, hd ** -0.5, r1, r2, sink))
+        out[f"masked_attention_prefill_mma_sync_{tokens}"] = {"us": round(us, 1), "tflops": round(4 * heads * hd * seen / us / 1e6, 1),
+                                                              "frac_bf16": round(4 * heads * hd * seen / us / 1e6 / pk["bf16_tflops"], 4)}
+        us = timed(lambda: api.attention_masked_prefill_tc(q, o, g, 0.7, m.k, m.v, ctx.plans[plans[1].key], ctx.cu_q, ctx.seq_pos0,
+                                                           ctx.tables[m.group], heads, kv_heads, hd, None, chunk, hd ** -0.5, r1, r2, sink))
         out[f"masked_attention_prefill_{tokens}"] = {"us": round(us, 1), "tflops": round(4 * heads * hd * seen / us / 1e6, 1),
                                                      "frac_bf16": round(4 * heads * hd * seen / us / 1e6 / pk["bf16_tflops"], 4)}
         full = tokens * (tokens + 1) // 2

@@ -731,6 +731,42 @@ def attention_masked_prefill_bf16(q, out, gate, out_scale, k_store, v_store, til
            "attention_masked_prefill_bf16")
 
 
+def masked_tc_takes(q, out, gate, head_dim, v_head_dim):
+    """Whether the tcgen05 prefill attention in its masked build takes these operands: equal head sizes of
+    64 or 128, rows a multiple of 8 elements apart and on 16-byte boundaries."""
+    if head_dim != v_head_dim or head_dim not in TC_ATTENTION_HEAD_DIMS:
+        return False
+    return all(t is None or (t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0) for t in (q, out, gate))
+
+
+def attention_masked_prefill_tc(q, out, gate, out_scale, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads,
+                                n_kv_heads, head_dim, window, chunk, scale, r1=None, r2=None, sink=None):
+    """``attention_masked`` for ragged query portions on tcgen05 tensor cores (bfloat16, equal head sizes of
+    64 or 128): the masked build of ``attention_prefill_tc``'s kernel. ``tiles`` lists 128-row tiles."""
+    global _tc_err
+    _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16), _need_rows(gate, "gate", torch.bfloat16)
+    _need(tiles, "tiles", torch.int32, 2), _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", torch.bfloat16, 4), _need(v_store, "v_store", torch.bfloat16, 4)
+    _need(r1, "r1", torch.float32, 1), _need(r2, "r2", torch.float32, 1), _need(sink, "sink", torch.float32, 1)
+    if n_heads % n_kv_heads or (r1 is None) != (r2 is None) or not masked_tc_takes(q, out, gate, head_dim, head_dim) \
+            or k_store.shape != v_store.shape:
+        raise KernelError("attention_masked_prefill_tc: head sizes, head counts or row strides not supported")
+    if _tc_err is None:
+        _tc_err = torch.zeros(1, dtype=torch.int32, device=q.device)
+    stream = _stream_ptr()
+    sched = _attn_sched.get(stream)
+    if sched is None:
+        sched = _attn_sched[stream] = torch.zeros(2, dtype=torch.int32, device=q.device)
+    lib = _lib("attention_tc.cu", {"HD": head_dim, "DK_MASKED": 1})
+    _check(lib, lib.dk_attn_prefill_tc_masked(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), _p(gate),
+                                              c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
+                                              _p(k_store), _p(v_store), c_longlong(q.shape[0]), c_longlong(k_store.shape[0]),
+                                              _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0), _p(page_table),
+                                              page_table.shape[1], n_heads, n_kv_heads, int(window or 0), int(chunk or 0),
+                                              c_float(scale), _p(r1), _p(r2), _p(sink), _p(_tc_err), _p(sched),
+                                              c_void_p(stream)), "attention_masked_prefill_tc")
+
+
 def masked_decode_span(n_heads, n_kv_heads, head_dim, window, chunk, table_pages):
     """The most keys a row of a decode step can see (chunk, window, or what the page table can hold), or
     None when the scores of a kv head's query heads over that many keys do not fit a block's shared memory."""

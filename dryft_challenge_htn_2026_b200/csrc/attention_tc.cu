@@ -50,6 +50,15 @@
 // heavy ones start first and the light ones fill the end.
 // Every mbarrier wait is bounded; a wait that runs out stores a code in *err, and the block still
 // frees its tensor memory and returns.
+//
+// Built with -DDK_MASKED=1 the same kernel is the prefill attention of mixers with further options (its
+// entry point is then dk_attn_prefill_tc_masked): a chunk mask beside the window (a query sees only keys
+// of its own chunk of ``chunk`` positions), a logarithmic distance bias taken off every score in the log2
+// domain, r1 * log2(1 + r2 * (i - j)) (from a table of the step's distances that each softmax warp makes
+// for itself: a shared-memory read a score instead of a logarithm), a sink
+// (2^(sink * log2 e - m) joins the row's denominator at the end), an output gate and a constant factor
+// on the normalised row, and q, gate and out as rows of wider matrices. The plain build has none of this
+// code.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -58,6 +67,9 @@
 #error "compile with -DHD=64 or -DHD=128"
 #endif
 static_assert(HD == 64 || HD == 128, "tensor-core prefill attention is built for head sizes 64 and 128");
+#ifndef DK_MASKED
+#define DK_MASKED 0
+#endif
 
 namespace {
 
@@ -71,6 +83,7 @@ constexpr int TMEM_ALLOC = 2 * BN + 128 <= 256 ? 256 : 512;   // S0 | S1 | O; al
 constexpr int OC = 32;                            // columns of O a thread handles at a time
 constexpr int HALVES = HD / 64;                   // 64-column swizzle atoms across the head
 constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;   // Q tile; one stage of K or of V
+constexpr int BIAS_TAB = 96;                      // distances a warp's 32 rows meet in a step of 64 keys (95), rounded up
 constexpr int Q_ATOM_BYTES = BM * 128;            // the 128 query rows of one 64-column atom
 constexpr int KV_ATOM_BYTES = BN * 128;           // the key rows of one 64-column atom
 #ifndef DK_WAIT_CYCLES
@@ -186,6 +199,20 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+#if DK_MASKED
+// first key a query at position pos may see: the start of its window or of its chunk, whichever is later
+__device__ __forceinline__ int first_key(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+#endif
+// log2(x), one MUFU instruction
+__device__ __forceinline__ float lg2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 // maximum of three, one instruction
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -208,7 +235,12 @@ __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, bf16* out, const int* tiles, int n_items, const int* cu_q,
                        const int* seq_pos0, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
-                       int* err, int* sched) {
+                       int* err, int* sched
+#if DK_MASKED
+                       , long long ldo, const bf16* gate, long long ldg, float out_scale, int chunk,
+                       const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink
+#endif
+                       ) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
     const uint32_t q_s = smem_u32(smem), k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES;   // Q, K stages 0 1, V stages 0 1
@@ -257,7 +289,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         it.flat0 = cu_q[seq] + it.q0;                      // first flat row of this tile
         it.pt = page_table + (size_t)seq * pt_stride;
         it.min_pos = it.pos0 + it.q0, it.max_pos = it.min_pos + it.rows_here - 1;
+#if DK_MASKED
+        it.blk_lo = first_key(it.min_pos, window, chunk) / BN;    // the first key a row sees never moves back as the position grows
+#else
         it.blk_lo = window > 0 ? max(0, it.min_pos - window + 1) / BN : 0;
+#endif
         it.n_blk = it.max_pos / BN - it.blk_lo + 1;
         return it;
     };
@@ -372,13 +408,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int r = threadIdx.x;                           // row within the tile = tensor-memory lane
         const bool valid = r < rows_here;
         const int qpos = pos0 + q0 + r;
+#if DK_MASKED
+        const int key_lo = first_key(qpos, window, chunk);
+        const int tile_lo = first_key(cur.max_pos, window, chunk);      // a step wholly at or after it is seen by every row
+        const float b1 = r1 ? r1[h] : 0.f, b2 = r1 ? r2[h] : 0.f;
+        // The bias of a step depends on the distance only, and the 32 rows of a warp meet 32 + 63 distances in a
+        // step of 64 keys: each lane works out three of them (one logarithm each) into a table of the warp's own,
+        // and a score then costs one shared-memory read instead of a logarithm. Two tables a warp, in turn.
+        float* bias_tab = reinterpret_cast<float*>(bars + 14) + (warp & 3) * (2 * BIAS_TAB);
+#else
         const int key_lo = window > 0 ? max(0, qpos - window + 1) : 0;
+#endif
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_blk && ok; i++) {
             const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
             const int key0 = (blk_lo + i) * BN;
+#if DK_MASKED
+            {   // this step's bias table, while S is still on its way (zeros without a bias)
+                float* tw = bias_tab + (t & 1) * BIAS_TAB;
+                const int d_first = min_pos + (warp & 3) * 32 - key0 - (BN - 1);
+                for (int k = lane; k < BIAS_TAB; k += 32)
+                    tw[k] = b1 != 0.f ? b1 * lg2(fmaf(b2, (float)max(d_first + k, 0), 1.f)) : 0.f;
+                __syncwarp();
+            }
+#endif
             if (!mbar_wait(bar_s + b, ph)) { ok = false; break; }
             fence_after();
             uint32_t v[CPT];
@@ -386,6 +441,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int c = 0; c < CPT; c += 32) tmem_ld32(t_s + lane_off + b * BN + c, *reinterpret_cast<uint32_t(*)[32]>(v + c));
             tmem_wait_ld();
             // every key of the step visible to every row of the tile: no per-element test
+#if DK_MASKED
+            const bool open = window <= 0 && key0 + BN - 1 <= min_pos && key0 >= tile_lo;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            // scores leave this loop in the log2 domain with the distance bias taken off: the bias of row lane, key j
+            // of the step sits at tab[lane + 63 - j] (distance = first distance of the warp in this step + that index)
+            const float* tab = bias_tab + (t & 1) * BIAS_TAB + lane + (BN - 1);
+            if (open) {
+#pragma unroll
+                for (int j = 0; j < CPT; j++) {
+                    const float x = fmaf(__uint_as_float(v[j]), sl2, -tab[-j]);
+                    v[j] = __float_as_uint(x);
+                    mx4[j & 3] = fmaxf(mx4[j & 3], x);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < CPT; j++) {
+                    const int key = key0 + j;
+                    float x = fmaf(__uint_as_float(v[j]), sl2, -tab[-j]);
+                    x = (valid && key <= qpos && key >= key_lo) ? x : -INFINITY;
+                    v[j] = __float_as_uint(x);
+                    mx4[j & 3] = fmaxf(mx4[j & 3], x);
+                }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+#else
             const bool open = window <= 0 && (blk_lo + i) * BN + BN - 1 <= min_pos;
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (open) {
@@ -401,6 +481,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // sl2 > 0: scaling keeps the order
+#endif
             float m_new = fmaxf(m, mx);
             // a maximum that moved by less than 8 (a factor 256) keeps the old reference: P stays well inside
             // float32 / bfloat16 range, the final O / l is the same, and O need not be rescaled
@@ -427,7 +508,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t p[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT; j += 2) {
+#if DK_MASKED
+                const float e0 = ex2(__uint_as_float(v[j]) - ms), e1 = ex2(__uint_as_float(v[j + 1]) - ms);
+#else
                 const float e0 = ex2(fmaf(__uint_as_float(v[j]), sl2, -ms)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sl2, -ms));
+#endif
                 sum4[(j >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
                 p[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
@@ -442,8 +527,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok) ok = mbar_wait(bar_o + ((step + n_blk - 1) & 1), ((step + n_blk - 1) >> 1) & 1);
         if (ok) {
             fence_after();
+#if DK_MASKED
+            float den = l;
+            if (sink != nullptr) den += ex2(sink[h] * 1.4426950408889634f - m);   // m is the row's reference, finite for a row that exists
+            const float inv = den > 0.f ? out_scale / den : 0.f;
+            bf16* dst = out + (size_t)(flat0 + r) * ldo + (size_t)h * HD;
+            const bf16* gr = gate != nullptr ? gate + (size_t)(flat0 + r) * ldg + (size_t)h * HD : nullptr;
+#else
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(flat0 + r) * nh + h) * HD;
+#endif
 #pragma unroll 1
             for (int c = 0; c < HD; c += OC) {
                 uint32_t o[OC];
@@ -454,9 +547,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     for (int j = 0; j < OC; j += 8) {
                         uint4 pk;
                         __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#if DK_MASKED
+                        uint4 gk = make_uint4(0u, 0u, 0u, 0u);
+                        if (gr != nullptr) gk = *reinterpret_cast<const uint4*>(gr + c + j);
+                        const bf16* g8 = reinterpret_cast<const bf16*>(&gk);
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            float x0 = __uint_as_float(o[j + 2 * u]) * inv, x1 = __uint_as_float(o[j + 2 * u + 1]) * inv;
+                            if (gr != nullptr) {
+                                x0 = __fdividef(x0, 1.f + __expf(-__bfloat162float(g8[2 * u])));
+                                x1 = __fdividef(x1, 1.f + __expf(-__bfloat162float(g8[2 * u + 1])));
+                            }
+                            pp[u] = __floats2bfloat162_rn(x0, x1);
+                        }
+#else
 #pragma unroll
                         for (int u = 0; u < 4; u++)
                             pp[u] = __floats2bfloat162_rn(__uint_as_float(o[j + 2 * u]) * inv, __uint_as_float(o[j + 2 * u + 1]) * inv);
+#endif
                         *reinterpret_cast<uint4*>(dst + c + j) = pk;
                     }
                 }
@@ -495,12 +603,13 @@ EncodeTiled encoder() {
     return fn;
 }
 
-// Row-major bf16 matrix [rows, cols]: boxes of box_rows x 64 columns, 128-byte swizzle, zero fill.
-int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+// Row-major bf16 matrix [rows, cols] (rows ``ld`` elements apart; 0: cols): boxes of box_rows x 64 columns,
+// 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows, long long ld = 0) {
     EncodeTiled enc = encoder();
     if (!enc) return (int)cudaErrorNotSupported;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint64_t strides[1] = {(cuuint64_t)(ld > 0 ? ld : cols) * 2};
     cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
@@ -513,6 +622,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 
 DK_EXPORT int dk_attn_tc_head_dim() { return HD; }
 
+#if !DK_MASKED
 // q, out [n_tok, nh*HD] bf16; k_store, v_store [n_pages, nkv, 64, HD] bf16; tiles [n_tiles][2] =
 // (sequence, first query of a 128-row tile within its chunk); err: device int for a wait that ran out;
 // sched: two device ints, zero (the kernel leaves them zero), not shared with a launch on another stream.
@@ -543,3 +653,39 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
     return dk_launch(attn_prefill_tc_kernel, dim3(blocks), dim3(THREADS), smem, st, mq, mk, mv, (bf16*)out, tiles, (int)n_items,
                      cu_q, seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err, sched);
 }
+#else
+// As dk_attn_prefill_tc with the options of the masked build: q, gate and out are rows of wider matrices
+// (ldq, ldg, ldo elements apart, multiples of 8, on 16-byte boundaries); gate, r1/r2 and sink may be null.
+DK_EXPORT int dk_attn_prefill_tc_masked(const void* q, long long ldq, void* out, long long ldo, const void* gate, long long ldg,
+                                        float out_scale, const void* k_store, const void* v_store, long long n_tok,
+                                        long long n_pages, const int* tiles, int n_tiles, const int* cu_q, const int* seq_pos0,
+                                        const int* page_table, int pt_stride, int nh, int nkv, int window, int chunk, float scale,
+                                        const float* r1, const float* r2, const float* sink, int* err, int* sched,
+                                        cudaStream_t st) {
+    if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1 || ldq % 8 || ldo % 8 || (gate && ldg % 8) ||
+        ((uintptr_t)q | (uintptr_t)out | (uintptr_t)gate) % 16 != 0)
+        return (int)cudaErrorInvalidValue;
+    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 14 * sizeof(uint64_t) + 4 * 2 * BIAS_TAB * sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr = true;
+    }
+    CUtensorMap mq, mk, mv;
+    int e = make_map(&mq, q, n_tok, (long long)nh * HD, BM, ldq);
+    if (!e) e = make_map(&mk, k_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
+    if (!e) e = make_map(&mv, v_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
+    if (e) return e;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long n_items = (long long)n_tiles * nh;
+    if (n_items > 0x7fffffffLL - 4 * sms) return (int)cudaErrorInvalidValue;
+    const long long slots = (long long)BLOCKS_PER_SM * sms;
+    const int blocks = (int)(n_items < slots ? n_items : slots);
+    return dk_launch(attn_prefill_tc_kernel, dim3(blocks), dim3(THREADS), smem, st, mq, mk, mv, (bf16*)out, tiles, (int)n_items,
+                     cu_q, seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err, sched, ldo,
+                     (const bf16*)gate, ldg, out_scale, chunk, r1, r2, sink);
+}
+#endif

@@ -3,7 +3,9 @@ window, a logarithmic distance bias, a sink in the softmax's denominator and an 
 switched on by its specification; key and value heads may differ in size.
 
 forward = one fused projection [q; k; v; gate] -> k and v into the cache -> attention over the cache
-with the gate in its epilogue -> output projection. The part also runs as a branch of a
+with the gate in its epilogue -> output projection. Kernels: bfloat16 prompts with equal head sizes of 64
+or 128 on tcgen05 tensor cores, other head sizes in steps of 16 on mma.sync, single tokens by a kernel of
+their own, and float32 (or any other size) on the float32-arithmetic kernel that serves every phase. The part also runs as a branch of a
 ``ParallelMixer``, which does the projections of all its branches in one product each: ``mix`` takes
 the projected rows and leaves scale * (gated heads) where the caller wants them.
 """
@@ -38,9 +40,12 @@ class MaskedAttention(Part):
         # head sizes) runs on the float32-arithmetic kernel, which serves every phase
         self.tensor_core = rt.dtype == torch.bfloat16 and api.masked_bf16_takes(s.head_dim, s.v_head_dim)
         self.tiles = QueryTiles(api.MASKED_TILE_ROWS) if self.tensor_core else None
+        # equal head sizes of 64 or 128: prompts run on the tcgen05 kernel (its masked build), in tiles of 128 queries
+        self.tc_tiles = QueryTiles(api.TC_TILE_ROWS) if self.tensor_core and s.head_dim == s.v_head_dim \
+            and s.head_dim in api.TC_ATTENTION_HEAD_DIMS else None
 
     def step_plans(self):
-        return [self.tiles] if self.tiles is not None else []
+        return [t for t in (self.tiles, self.tc_tiles) if t is not None]
 
     def param_decls(self):
         s = self.spec
@@ -86,6 +91,10 @@ class MaskedAttention(Part):
         if writes:
             api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
+        if self.tc_tiles is not None and not ctx.is_decode and api.masked_tc_takes(q, mid, gate, s.head_dim, s.v_head_dim):
+            return api.attention_masked_prefill_tc(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tc_tiles.key], ctx.cu_q,
+                                                   ctx.seq_pos0, table, s.num_heads, s.num_kv_heads, s.head_dim, s.window,
+                                                   s.chunk, s.scale, self.r1, self.r2, self.sink)
         if self.tensor_core and not ctx.is_decode:
             return api.attention_masked_prefill_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tiles.key], ctx.cu_q,
                                                      ctx.seq_pos0, table, *sizes, self.r1, self.r2, self.sink)
