@@ -408,3 +408,40 @@ def test_trace_replay_of_a_ragged_schedule(tmp_path, dtype):
             got = torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(len(rows), vocab))
             for r, (i, p) in enumerate(rows):
                 assert float((got[r].double() - ref[i][p]).abs().max()) <= tol(dtype, ref[i]), (s["step"], i, p)
+
+
+def test_command_line_generates_with_a_nilivik_model(tmp_path):
+    """The command line as a user runs it: random weights from a config.json of this design, the tokens it
+    prints against the plain implementation's greedy tokens, then the saved folder in bfloat16 with JSON records."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from dryft_challenge_htn_2026_b200.cli import random_prompts
+    from helpers import ROOT
+
+    def run_cli(*args):
+        env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        return subprocess.run([sys.executable, "-m", "dryft_challenge_htn_2026_b200.cli", *args], capture_output=True,
+                              text=True, env=env, cwd=str(ROOT), timeout=900)
+
+    cfg = dk.config_from_dict(SHAPES["P"])
+    cfg.save(str(tmp_path))
+    model_dir = str(tmp_path / "model")
+    r = run_cli("--random-weights", str(tmp_path / "config.json"), "--save-model", model_dir, "--seed", "3", "--dtype", "float32",
+                "--shapes", "2,30,6", "--samples", "1", "--print-tokens")
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = [l for l in r.stdout.splitlines() if l.startswith("tokens 2,30,6 seq ")]
+    assert len(lines) == 2
+    pcfg, t = plain.read_model(model_dir, torch.float64)
+    prompts = random_prompts(2, 30, 1, cfg.vocab, False)
+    for i, line in enumerate(lines):
+        emitted = [int(x) for x in line.split(":")[1].split()]
+        if emitted != plain.greedy(pcfg, t, prompts[i], 6):                 # a near-tie may flip: then the gap is rounding-small
+            logits = plain.forward(pcfg, t, prompts[i] + emitted[:-1])[len(prompts[i]) - 1:]
+            gap = float((logits.max(-1).values - logits.gather(1, torch.tensor(emitted).view(-1, 1)).squeeze(1)).max())
+            assert gap < 1e-3, (emitted, gap)
+    r = run_cli("--model", model_dir, "--shapes", "3,70,5", "--samples", "1", "--ragged", "--json")
+    assert r.returncode == 0, r.stdout + r.stderr
+    records = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [x["shape"] for x in records] == ["3,70,5"] and records[0]["tok_s"] > 0
