@@ -305,18 +305,19 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
 
 
 # ---------------------------------------------------------------------------------------- products
-MODE_STORE, MODE_STORE_F32, MODE_SILU = 0, 1, 2
+MODE_STORE, MODE_STORE_F32, MODE_SILU, MODE_XIELU = 0, 1, 2, 3
 
 
-def sgemm(x, w, out, mode=MODE_STORE):
-    """float32 out = x . w^T on CUDA cores; mode MODE_SILU: w = [gate; up], out = silu(g) * u."""
+def sgemm(x, w, out, mode=MODE_STORE, act=(0.0, 0.0)):
+    """float32 out = x . w^T on CUDA cores; mode MODE_SILU: w = [gate; up], out = silu(g) * u; mode MODE_XIELU:
+    out = xielu(x . w^T) with the constants ``act`` = (alpha_pos, alpha_neg)."""
     _need(x, "x", torch.float32, 2), _need(w, "w", torch.float32, 2), _need(out, "out", torch.float32, 2)
     M, K = x.shape
     N = out.shape[1]
     if w.shape != ((2 * N if mode == MODE_SILU else N), K) or out.shape[0] != M:
         raise KernelError(f"sgemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
     lib = _lib("gemm.cu")
-    _check(lib, lib.dk_sgemm(_p(x), _p(w), _p(out), M, N, K, mode, _stream()), "sgemm")
+    _check(lib, lib.dk_sgemm(_p(x), _p(w), _p(out), M, N, K, mode, c_float(act[0]), c_float(act[1]), _stream()), "sgemm")
 
 
 # ---------------------------------------------------------------------------------------- sampling
@@ -383,7 +384,7 @@ def stream_plan(M, N, K, mode, allow_partial=False):
         sk *= 2
         if sk > 64:
             return None
-    can_slice = allow_partial and mode != MODE_SILU
+    can_slice = allow_partial and mode not in (MODE_SILU, MODE_XIELU)
     if sk > 1 and not can_slice:
         return None
     if can_slice:
@@ -399,7 +400,7 @@ def stream_plan(M, N, K, mode, allow_partial=False):
     return sk, blocks, warps
 
 
-def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
+def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, act=(0.0, 0.0)):
     """The weight-streaming skinny product (asynchronous copies into shared-memory rings,
     tensor-core multiply) for at most 16 rows of x and K a multiple of 16. Returns ``out`` [M, N]
     (bfloat16 for MODE_STORE and MODE_SILU, float32 for MODE_STORE_F32), or, when the plan splits K
@@ -417,8 +418,8 @@ def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
                           f"(the {M} rows of a slice of x must fit a block's shared memory, and there is a block per slice at least)")
     ws = None
     if sk > 1:
-        if mode == MODE_SILU:
-            raise KernelError("gemv_stream: the SiLU epilogue cannot be split over K")
+        if mode in (MODE_SILU, MODE_XIELU):
+            raise KernelError("gemv_stream: an activation in the epilogue cannot be split over K")
         ws = torch.empty((sk, M, N), dtype=torch.float32, device=w.device)
     else:
         want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
@@ -427,7 +428,8 @@ def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
         elif out.dtype != want or tuple(out.shape) != (M, N):
             raise KernelError(f"gemv_stream: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
     lib = _lib("gemv_stream.cu")
-    _check(lib, lib.dk_gemv_stream(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, warps, _stream()), "gemv_stream")
+    _check(lib, lib.dk_gemv_stream(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, warps, c_float(act[0]),
+                                   c_float(act[1]), _stream()), "gemv_stream")
     return Partial(ws) if sk > 1 else out
 
 
@@ -435,7 +437,7 @@ def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
 _tc_err = None
 
 
-def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None):
+def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None, act=(0.0, 0.0)):
     """out = x . w^T (mode MODE_STORE, MODE_STORE_F32) or silu(x . gate^T) * (x . up^T) (mode
     MODE_SILU, w = [gate; up]) on tcgen05 tensor cores, TMA-fed, float32 accumulation in tensor
     memory. ``plan`` = (weight rows per tile, one of TC_TILE_HEIGHTS; slices of K): with more than
@@ -445,8 +447,11 @@ def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None):
     M, K = x.shape
     N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
     bn, sk = plan or (256, 1)
+    xielu = mode == MODE_XIELU          # the plain product with the activation on its finished sums
+    if xielu:
+        mode = MODE_STORE
     if K % 8 or w.shape[1] != K or mode not in (MODE_STORE, MODE_STORE_F32, MODE_SILU) \
-            or bn not in TC_TILE_HEIGHTS:
+            or bn not in TC_TILE_HEIGHTS or (xielu and sk != 1):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} mode {mode} not supported (K % 8 == 0)")
     kb = (K + 63) // 64
     if sk < 1 or (sk > 1 and (mode != MODE_STORE or (sk - 1) * ((kb + sk - 1) // sk) >= kb)):
@@ -467,7 +472,8 @@ def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None):
         _tc_err = torch.zeros(1, dtype=torch.int32, device=x.device)
     lib = _lib("gemm_tc.cu")
     _check(lib, lib.dk_gemm_tc(_p(x), _p(w), _p(None if ws is not None else out), M, N, K,
-                               MODE_STORE if mode == MODE_STORE_F32 else mode, _p(_tc_err), sk, _p(ws), bn, _stream()),
+                               MODE_STORE if mode == MODE_STORE_F32 else mode, _p(_tc_err), sk, _p(ws), bn, int(xielu),
+                               c_float(act[0]), c_float(act[1]), _stream()),
            "gemm_tc")
     return Partial(ws) if sk > 1 else out
 
@@ -524,6 +530,8 @@ def skinny_tc_plan(M, N, K, mode, allow_partial=False):
             tiles = (N + bn // 2 - 1) // (bn // 2)
             return bn * -(-tiles // sms)
         return min(TC_TILE_HEIGHTS, key=lambda bn: (span(bn), bn)), 1
+    if mode == MODE_XIELU:        # no slices (the activation needs whole sums): the tile height with the smallest unit
+        return min(TC_TILE_HEIGHTS, key=lambda bn: (bn * -(-((N + bn - 1) // bn) // sms), bn)), 1
     if mode != MODE_STORE or not allow_partial:
         return 256, 1
     plans = []
@@ -776,9 +784,15 @@ def masked_decode_span(n_heads, n_kv_heads, head_dim, window, chunk, table_pages
 
 
 def attention_masked_decode_bf16(q, out, gate, out_scale, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads,
-                                 head_dim, v_head_dim, window, chunk, scale, span, r1=None, r2=None, sink=None):
+                                 head_dim, v_head_dim, window, chunk, scale, span, r1=None, r2=None, sink=None,
+                                 k_new=None, v_new=None):
     """``attention_masked`` for one query token per sequence (bfloat16 storage, float32 arithmetic): a block
-    per (kv head, row) for all query heads of the group. ``span`` from ``masked_decode_span``."""
+    per (kv head, row) for all query heads of the group. ``span`` from ``masked_decode_span``. With
+    ``k_new`` / ``v_new`` (rows of the step's projection) the kernel writes each token's key and value into
+    the cache itself before it reads it."""
+    _need_rows(k_new, "k_new", torch.bfloat16), _need_rows(v_new, "v_new", torch.bfloat16)
+    if (k_new is None) != (v_new is None) or (k_new is not None and k_new.stride(0) != v_new.stride(0)):
+        raise KernelError("attention_masked_decode_bf16: k_new and v_new come together, as rows of one matrix")
     _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16), _need_rows(gate, "gate", torch.bfloat16)
     _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
     _need(k_store, "k_store", torch.bfloat16), _need(v_store, "v_store", torch.bfloat16)
@@ -791,7 +805,8 @@ def attention_masked_decode_bf16(q, out, gate, out_scale, k_store, v_store, row_
                                                c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
                                                _p(k_store), _p(v_store), _p(row_pos), _p(page_table), page_table.shape[1],
                                                q.shape[0], n_heads, n_kv_heads, int(window or 0), int(chunk or 0),
-                                               c_float(scale), _p(r1), _p(r2), _p(sink), int(span), _stream()),
+                                               c_float(scale), _p(r1), _p(r2), _p(sink), int(span), _p(k_new), _p(v_new),
+                                               c_longlong(k_new.stride(0) if k_new is not None else 0), _stream()),
            "attention_masked_decode_bf16")
 
 

@@ -236,7 +236,7 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
                           float out_scale, const bf16* k_store, const bf16* v_store, const int* row_pos,
                           const int* page_table, int pt_stride, int nh, int nkv, int window, int chunk, float scale,
                           const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink,
-                          int span) {
+                          int span, const bf16* k_new, const bf16* v_new, long long ldkv, bf16* k_out, bf16* v_out) {
     extern __shared__ __align__(16) float fsm[];
     const int G = nh / nkv, kvh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
     float* red = fsm;                       // [key split][4 heads][HDV]
@@ -251,6 +251,13 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
     }
     const int lo = first_key(pos, window, chunk), n = pos - lo + 1;
     const int* pt = page_table + (size_t)b * pt_stride;
+    if (k_new != nullptr) {   // the token's own key and value go into the cache here, by the block that reads them first
+        const int page = pt[pos / DK_PAGE];
+        for (int i = tid; i < HD; i += MD_THREADS)
+            k_out[kv_offset(page, nkv, kvh, pos % DK_PAGE, HD) + i] = k_new[(size_t)b * ldkv + (size_t)kvh * HD + i];
+        for (int i = tid; i < HDV; i += MD_THREADS)
+            v_out[kv_offset(page, nkv, kvh, pos % DK_PAGE, HDV) + i] = v_new[(size_t)b * ldkv + (size_t)kvh * HDV + i];
+    }
     for (int i = tid; i < G * HD; i += MD_THREADS) qs[i] = __bfloat162float(q[(size_t)b * ldq + (size_t)kvh * G * HD + i]);
     __syncthreads();
     // scores: a thread per key, the key row read in 16-byte pieces, four heads from one read
@@ -368,12 +375,15 @@ DK_EXPORT int dk_attn_masked_prefill_bf16(const void* q, long long ldq, void* ou
                      sink);
 }
 
+// k_new, v_new (or null): rows [n_rows, nkv*HD] / [n_rows, nkv*HDV] of the step's projection, ldkv elements apart,
+// which the kernel stores at each row's position before it reads the cache (no separate cache-write launch).
 // span: the most keys any row sees (the chunk, the window, or the longest sequence's length, rounded up by the caller)
 DK_EXPORT int dk_attn_masked_decode_bf16(const void* q, long long ldq, void* out, long long ldo, const void* gate,
                                          long long ldg, float out_scale, const void* k_store, const void* v_store,
                                          const int* row_pos, const int* page_table, int pt_stride, int n_rows, int nh,
                                          int nkv, int window, int chunk, float scale, const float* r1, const float* r2,
-                                         const float* sink, int span, cudaStream_t st) {
+                                         const float* sink, int span, const void* k_new, const void* v_new, long long ldkv,
+                                         cudaStream_t st) {
     if (nh % nkv != 0) return (int)cudaErrorInvalidValue;
     const int G = nh / nkv;
     const size_t smem = sizeof(float) * ((size_t)MD_RED_FLOATS + (size_t)G * HD + (size_t)G * span);
@@ -385,5 +395,6 @@ DK_EXPORT int dk_attn_masked_decode_bf16(const void* q, long long ldq, void* out
     }
     return dk_launch(attn_masked_decode_kernel, dim3(nkv, n_rows), dim3(MD_THREADS), smem, st, (const bf16*)q, ldq, (bf16*)out,
                      ldo, (const bf16*)gate, ldg, out_scale, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table,
-                     pt_stride, nh, nkv, window, chunk, scale, r1, r2, sink, span);
+                     pt_stride, nh, nkv, window, chunk, scale, r1, r2, sink, span, (const bf16*)k_new, (const bf16*)v_new, ldkv,
+                     (bf16*)k_store, (bf16*)v_store);
 }

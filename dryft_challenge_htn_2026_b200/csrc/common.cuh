@@ -49,6 +49,12 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return red[32];
 }
 
+// xIELU: f(z) = ap z^2 + z/2 for z > 0, an (e^z - 1 - z) + z/2 otherwise (ap, an > 0 are made on the host from the two
+// learned numbers); arithmetic in float32. The row kernel and the epilogues of the three products share it.
+__device__ __forceinline__ float xielu_f(float z, float ap, float an) {
+    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+}
+
 // Programmatic dependent launch. A kernel launched with the attribute may start while its
 // predecessor in the stream drains; pdl_wait() blocks until the predecessor has finished and its
 // writes are visible, so nothing the predecessor (or any earlier kernel) wrote may be read, and

@@ -651,10 +651,7 @@ DK_EXPORT int dk_softcap(float* x, long long n, float cap, cudaStream_t st) {
     return dk_launch(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, (size_t)n, cap);
 }
 
-// xIELU: f(z) = ap z^2 + z/2 for z > 0, an (e^z - 1 - z) + z/2 otherwise; arithmetic in float32.
-__device__ __forceinline__ float xielu_f(float z, float ap, float an) {
-    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
-}
+// xIELU (common.cuh) as a kernel of its own, for the products that do not have it in their epilogue.
 
 template <typename T>
 __global__ void xielu_kernel(const T* z, T* out, size_t n, float ap, float an) {

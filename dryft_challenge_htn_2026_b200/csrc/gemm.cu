@@ -13,9 +13,9 @@
 #define SG_BN 64
 #define SG_BK 16
 
-template <bool SILU>
+template <bool SILU, bool XIELU>
 __global__ void __launch_bounds__(256)
-sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int N, int K) {
+sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int N, int K, float act_pos, float act_neg) {
     __shared__ float xs[SG_BK][SG_BM + 4];
     __shared__ float ws[SG_BK][SG_BN + 4];
     __shared__ float us[SILU ? SG_BK : 1][SG_BN + 4];
@@ -64,16 +64,19 @@ sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int
             if (m < M && n < N) {
                 float v = acc[i][j];
                 if (SILU) v = v / (1.f + expf(-v)) * acu[i][j];
+                if (XIELU) v = xielu_f(v, act_pos, act_neg);
                 out[(size_t)m * N + n] = v;
             }
         }
 }
 
-// mode 0/1: plain; mode 2: W has 2N rows [gate; up], out [M, N]
-DK_EXPORT int dk_sgemm(const float* x, const float* W, float* out, int M, int N, int K, int mode, cudaStream_t st) {
+// mode 0/1: plain; mode 2: W has 2N rows [gate; up], out [M, N]; mode 3: xIELU(x . W^T) with the two constants
+DK_EXPORT int dk_sgemm(const float* x, const float* W, float* out, int M, int N, int K, int mode, float act_pos, float act_neg,
+                       cudaStream_t st) {
     dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
-    if (mode == 2) return dk_launch(sgemm_kernel<true>, grid, dim3(256), 0, st, x, W, out, M, N, K);
-    return dk_launch(sgemm_kernel<false>, grid, dim3(256), 0, st, x, W, out, M, N, K);
+    if (mode == 2) return dk_launch(sgemm_kernel<true, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, 0.f, 0.f);
+    if (mode == 3) return dk_launch(sgemm_kernel<false, true>, grid, dim3(256), 0, st, x, W, out, M, N, K, act_pos, act_neg);
+    return dk_launch(sgemm_kernel<false, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, 0.f, 0.f);
 }
 
 // ----------------------------------------------------------------------------------- partial sums

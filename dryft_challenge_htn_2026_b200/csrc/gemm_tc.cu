@@ -145,6 +145,9 @@ struct QkvEpilogue {
     const int *row_pos, *row_seq, *page_table;
     int pt_stride, nh, nkv, hd, write_kv;
     float eps;
+    // mode 0 only: an activation on the finished sums before they are stored (never on partial sums): 1 = xIELU
+    int act;
+    float act_pos, act_neg;
 };
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -496,6 +499,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             f.z = __fdividef(f.z, 1.f + __expf(-f.z)) * up.z;
                             f.w = __fdividef(f.w, 1.f + __expf(-f.w)) * up.w;
                         }
+                        if (MODE == 0 && qe.act == 1 && ws == nullptr) {
+                            f.x = xielu_f(f.x, qe.act_pos, qe.act_neg), f.y = xielu_f(f.y, qe.act_pos, qe.act_neg);
+                            f.z = xielu_f(f.z, qe.act_pos, qe.act_neg), f.w = xielu_f(f.w, qe.act_pos, qe.act_neg);
+                        }
                         const int col = n0 + c;
                         if (col >= N) continue;
                         if (ws != nullptr) {
@@ -541,6 +548,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                         for (int i = 0; i < 32; i++) f[i] = __fdividef(f[i], 1.f + __expf(-f[i])) * __uint_as_float(u[i]);   // 2 ulp: far below the bf16 rounding that follows
                     }
+                }
+                if (MODE == 0 && qe.act == 1 && ws == nullptr && row < M) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) f[i] = xielu_f(f[i], qe.act_pos, qe.act_neg);
                 }
                 if (row < M && ws != nullptr) {   // float32 partial sums of this slice
                     float* dst = ws + ((size_t)slice * M + row) * N + n0 + c;
@@ -660,8 +671,12 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
 // slices of K (every slice at least one block of 64 columns; SK = 1: the product itself in
 // float32). bn: weight rows a tile, a multiple of 16 from 128 to 256 (mode 2: half of them gate
 // rows, half up rows): the planner picks the height whose tiles and slices load the SMs most evenly.
+// act = 1 (mode 0, SK = 1, bfloat16 out): xIELU with the two constants on the sums before they are stored.
 DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, int SK, float* ws,
-                         int bn, cudaStream_t st) {
+                         int bn, int act, float act_pos, float act_neg, cudaStream_t st) {
+    if (act != 0 && (act != 1 || mode != 0 || SK != 1 || ws != nullptr)) return (int)cudaErrorInvalidValue;
+    QkvEpilogue qe{};
+    qe.act = act, qe.act_pos = act_pos, qe.act_neg = act_neg;
     if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr || SK < 1) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)W) % 16 != 0) return (int)cudaErrorInvalidValue;
     const int k_blocks = (K + 63) / 64, k_per = (k_blocks + SK - 1) / SK;
@@ -669,7 +684,7 @@ DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, 
     if (ws != nullptr && mode != 0) return (int)cudaErrorInvalidValue;
 #define TILE_HEIGHT(BN)                                                                                          \
     if (bn == BN && mode == 2) return launch<BN, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st); \
-    if (bn == BN && mode == 0) return launch<BN, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st)
+    if (bn == BN && mode == 0) return launch<BN, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st, qe)
     TILE_HEIGHT(128); TILE_HEIGHT(144); TILE_HEIGHT(160); TILE_HEIGHT(176); TILE_HEIGHT(192);
     TILE_HEIGHT(208); TILE_HEIGHT(224); TILE_HEIGHT(240); TILE_HEIGHT(256);
 #undef TILE_HEIGHT
@@ -690,7 +705,7 @@ DK_EXPORT int dk_gemm_tc_qkv(const void* x, const void* W, int M, int K, int* er
          (uintptr_t)kn | (uintptr_t)cos_t | (uintptr_t)sin_t) % 16 != 0)
         return (int)cudaErrorInvalidValue;
     QkvEpilogue qe{(bf16*)q_out, (bf16*)k_store, (bf16*)v_store, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table,
-                   pt_stride, nh, nkv, hd, write_kv, eps};
+                   pt_stride, nh, nkv, hd, write_kv, eps, 0, 0.f, 0.f};
     if (hd == 128) return launch<256, 3>((const bf16*)x, (const bf16*)W, nullptr, M, (nh + 2 * nkv) * hd, K, err, 1, nullptr, st, qe);
     return launch<256, 4>((const bf16*)x, (const bf16*)W, nullptr, M, (nh + 2 * nkv) * hd, K, err, 1, nullptr, st, qe);
 }

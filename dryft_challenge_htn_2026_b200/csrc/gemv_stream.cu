@@ -82,7 +82,8 @@ __host__ __device__ constexpr size_t smem_bytes(int warps, int mr, int slice) {
 // bytes a ring slot holds in flight shrink with the tile, and the kernel lives on bytes in flight.)
 template <int MR, int MODE, int WARPS>
 __global__ void __launch_bounds__((WARPS + 1) * 32)
-gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK, int tiles) {
+gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK, int tiles,
+                   float act_pos, float act_neg) {
     __shared__ __align__(8) uint64_t x_bar;   // counts the bytes of x's rows as they land
     constexpr int THREADS = (WARPS + 1) * 32;
     constexpr int RED = WARPS * WR * MR;      // floats of one buffer of the warps' sums
@@ -187,6 +188,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
                         for (int w = 0; w < WARPS; w++) up += sums[w * (WR * MR) + (8 + i) * MR + j];
                         v = v / (1.f + expf(-v)) * up;
                     }
+                    if (MODE == 3) v = xielu_f(v, act_pos, act_neg);
                     if (SK > 1) ws[((size_t)slice * M + j) * N + n] = v;
                     else if (MODE == 1) reinterpret_cast<float*>(out)[(size_t)j * N + n] = v;
                     else reinterpret_cast<bf16*>(out)[(size_t)j * N + n] = __float2bfloat16_rn(v);
@@ -247,7 +249,8 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
 }
 
 template <int MR, int MODE, int WARPS>
-int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int K, int SK, int blocks, cudaStream_t st) {
+int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int K, int SK, int blocks, cudaStream_t st,
+           float act_pos = 0.f, float act_neg = 0.f) {
     const size_t smem = smem_bytes(WARPS, MR, slice_len(K, SK));
     if (smem > SMEM_LIMIT) return (int)cudaErrorInvalidValue;
     static size_t attr_smem = 0;
@@ -261,7 +264,7 @@ int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int
     blocks = blocks / SK * SK;
     if (blocks > tiles * SK) blocks = tiles * SK;
     return dk_launch(gemv_stream_kernel<MR, MODE, WARPS>, dim3(blocks), dim3((WARPS + 1) * 32), smem, st, x, W, out, ws, M, N, K,
-                     SK, tiles);
+                     SK, tiles, act_pos, act_neg);
 }
 
 }  // namespace
@@ -277,16 +280,18 @@ DK_EXPORT long long dk_gemv_stream_smem(int rows, int K, int SK, int warps) {
 // sums ws [SK][M][N], modes 0 and 1); `blocks` persistent blocks, at least SK, rounded down to a
 // multiple of SK; `warps` streaming warps a block, 4 or 8. Refused (cudaErrorInvalidValue) when the
 // rows of a slice do not fit the shared memory of a block of that shape.
+// Mode 3: as mode 0 with xIELU (constants act_pos, act_neg) on the sums before they are stored; SK = 1.
 DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws, int M, int N, int K, int mode, int SK,
-                             int blocks, int warps, cudaStream_t st) {
+                             int blocks, int warps, float act_pos, float act_neg, cudaStream_t st) {
     if (M < 1 || M > 16 || K % 16 != 0 || SK < 1 || blocks < SK || (warps != 4 && warps != 8)) return (int)cudaErrorInvalidValue;
-    if (mode < 0 || mode > 2 || (SK > 1 && (mode == 2 || ws == nullptr)) || !x) return (int)cudaErrorInvalidValue;
+    if (mode < 0 || mode > 3 || (SK > 1 && (mode >= 2 || ws == nullptr)) || !x) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)W) % 16 != 0) return (int)cudaErrorInvalidValue;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
 #define GS_MODE(MR, WARPS)                                                                       \
     if (mode == 0) return launch<MR, 0, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);        \
     if (mode == 1) return launch<MR, 1, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);        \
+    if (mode == 3) return launch<MR, 3, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st, act_pos, act_neg); \
     return launch<MR, 2, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);
 #define GS_CASE(MR)                   \
     if (warps == 4) { GS_MODE(MR, 4) } \

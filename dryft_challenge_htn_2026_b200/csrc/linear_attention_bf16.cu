@@ -304,6 +304,12 @@ DK_EXPORT int dk_linear_attention_chunk_bf16(void* q, void* k, void* v, long lon
     int e = dk_launch(silu_rows_kernel, dim3((unsigned)((items + 255) / 256), 3), dim3(256), 0, st, (bf16*)q, nh * HD, (bf16*)k,
                       nh * HD, (bf16*)v, nh * hdv, ld, n_rows);
     if (e != 0) return e;
-    if (hdv % 32 == 0) return launch_chunk<32>(q, k, v, ld, out, state, cu_q, seq_slot, decay, n_seq, nh, hdv, st);
+    // 32 value columns a block; 16 while that leaves SMs without a block (a block of 16 repeats Q K^T for half the
+    // columns, but the chain of a sequence's blocks is what the kernel's time is made of)
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (hdv % 32 == 0 && (long long)n_seq * nh * (hdv / 32) >= sms)
+        return launch_chunk<32>(q, k, v, ld, out, state, cu_q, seq_slot, decay, n_seq, nh, hdv, st);
     return launch_chunk<16>(q, k, v, ld, out, state, cu_q, seq_slot, decay, n_seq, nh, hdv, st);
 }

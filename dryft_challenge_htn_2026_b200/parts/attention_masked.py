@@ -88,9 +88,14 @@ class MaskedAttention(Part):
         k = proj[:, self.n_q:self.n_q + self.n_k]
         v = proj[:, self.n_q + self.n_k:self.n_q + self.n_k + self.n_v]
         gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
+        sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
+        span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1]) \
+            if self.tensor_core and ctx.is_decode else None
+        if span is not None:      # single tokens: the kernel stores each token's key and value itself
+            return api.attention_masked_decode_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, table, *sizes, span,
+                                                    self.r1, self.r2, self.sink, k if writes else None, v if writes else None)
         if writes:
             api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
-        sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
         if self.tc_tiles is not None and not ctx.is_decode and api.masked_tc_takes(q, mid, gate, s.head_dim, s.v_head_dim):
             return api.attention_masked_prefill_tc(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tc_tiles.key], ctx.cu_q,
                                                    ctx.seq_pos0, table, s.num_heads, s.num_kv_heads, s.head_dim, s.window,
@@ -98,11 +103,6 @@ class MaskedAttention(Part):
         if self.tensor_core and not ctx.is_decode:
             return api.attention_masked_prefill_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tiles.key], ctx.cu_q,
                                                      ctx.seq_pos0, table, *sizes, self.r1, self.r2, self.sink)
-        if self.tensor_core:
-            span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1])
-            if span is not None:
-                return api.attention_masked_decode_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, table, *sizes, span,
-                                                        self.r1, self.r2, self.sink)
         api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, *sizes, self.r1, self.r2,
                              self.sink)
 

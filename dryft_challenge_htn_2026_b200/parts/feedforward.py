@@ -6,7 +6,7 @@ import torch
 from ..config.specs import DenseMLPSpec, GatedMLPSpec
 from ..csrc import api
 from .base import ParamDecl, Part, register_part
-from .linear import SILU, linear
+from .linear import SILU, XIELU, linear
 
 
 class GatedMLP(Part):
@@ -42,8 +42,8 @@ register_part(GatedMLPSpec, GatedMLP)
 class DenseMLP(Part):
     """down(act(up(x))) with the xIELU activation: act(z) = ap z^2 + z/2 for z > 0 and
     an (e^z - 1 - z) + z/2 otherwise, ap = softplus(p), an = 1/2 + softplus(q) from the two learned
-    numbers of ``act`` (worked out once, in float64, when the tensors are bound). In the float32 path and
-    in decode steps the activation is a kernel of its own between the two products."""
+    numbers of ``act`` (worked out once, in float64, when the tensors are bound). The activation sits in
+    the epilogue of the up projection (every product kernel of the library has it as a mode)."""
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -69,8 +69,7 @@ class DenseMLP(Part):
         return [self.w_up, self.w_down]
 
     def forward(self, ctx, a):
-        z = linear(a, self.w_up)
-        api.xielu(z, z, self.alpha_pos, self.alpha_neg)
+        z = linear(a, self.w_up, XIELU, act=(self.alpha_pos, self.alpha_neg))
         return linear(z, self.w_down, allow_partial=True)
 
 

@@ -10,32 +10,37 @@ import torch
 
 from ..csrc import api
 
-STORE, STORE_F32, SILU = api.MODE_STORE, api.MODE_STORE_F32, api.MODE_SILU
+STORE, STORE_F32, SILU, XIELU = api.MODE_STORE, api.MODE_STORE_F32, api.MODE_SILU, api.MODE_XIELU
 
 
-def linear(x, w, mode=STORE, allow_partial=False):
+def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
     """mode STORE: [M, N] in x's dtype; STORE_F32: float32 (logits); SILU: w = [gate; up] rows,
-    returns silu(x.gate^T) * (x.up^T) of width N/2. ``allow_partial``: the caller can take
+    returns silu(x.gate^T) * (x.up^T) of width N/2; XIELU: xielu(x.w^T) with the constants ``act`` =
+    (alpha_pos, alpha_neg), in the product's epilogue wherever the product is this library's (after
+    the library's product a row kernel applies it). ``allow_partial``: the caller can take
     ``csrc.api.Partial`` (split-K partial sums, added up by the kernel that consumes them) instead
     of a tensor."""
     M, K = x.shape
     N = w.shape[0] // 2 if mode == SILU else w.shape[0]
     if x.dtype == torch.float32:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-        api.sgemm(x, w, out, mode)
+        api.sgemm(x, w, out, mode, act)
         return out
     if M <= api.STREAM_BEST_ROWS and K % 16 == 0:
         plan = api.stream_plan(M, N, K, mode, allow_partial)
         if plan is not None:
-            return api.gemv_stream(x, w, None, mode, plan)
+            return api.gemv_stream(x, w, None, mode, plan, act)
     if M <= api.TC_SKINNY_MAX_ROWS:
         # a decode step of up to 128 rows: weights streamed once by TMA, one 128-row tile of x,
         # K in slices so that the few weight tiles still cover the SMs
-        return api.gemm_tc(x, w, mode, None, api.skinny_tc_plan(M, N, K, mode, allow_partial))
+        return api.gemm_tc(x, w, mode, None, api.skinny_tc_plan(M, N, K, mode, allow_partial), act)
     if mode == STORE_F32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     if mode == SILU:
         return api.gemm_tc(x, w, mode, None, api.gated_tc_plan(M, N))   # TMA + tcgen05, SiLU*up fused into the epilogue
     if api.gemm_tc_fills_gpu(M, N):
-        return api.gemm_tc(x, w, mode)
-    return torch.mm(x, w.t())
+        return api.gemm_tc(x, w, mode, act=act)
+    out = torch.mm(x, w.t())
+    if mode == XIELU:
+        api.xielu(out, out, act[0], act[1])
+    return out
