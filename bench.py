@@ -463,10 +463,17 @@ def kernel_times(torch, dk, pk, heads, kv_heads, rh, chunk):
         o = torch.empty_like(q)
         keys = context - context // chunk * chunk + 1
         table = ctx.tables[m.group]
-        span = api.masked_decode_span(heads, kv_heads, hd, None, chunk, table.shape[1])
+        span = api.masked_decode_span(heads, kv_heads, hd, None, chunk, table.shape[1], batch)
+        mws = api.masked_decode_ws(batch, heads, hd, span[1], dev)
         us = timed(lambda: api.attention_masked_decode_bf16(q, o, g, 0.7, m.k, m.v, ctx.row_pos, table, heads, kv_heads, hd, hd, None,
-                                                            chunk, hd ** -0.5, span, r1, r2, sink))
+                                                            chunk, hd ** -0.5, span, r1, r2, sink, None, None, mws))
         moved = batch * kv_heads * keys * 2 * hd * 2
+        out[f"masked_attention_decode_block_kernel_b{batch}"] = {"us": round(us, 1), "keys": keys, "gbs": round(moved / us / 1e3, 1),
+                                                                 "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+        ns = api.masked_decode_splits(batch, kv_heads, heads // kv_heads, table.shape[1], None, chunk)
+        mws2 = api.attention_decode_ws(batch, heads, hd, ns, dev)
+        us = timed(lambda: api.attention_decode_masked_bf16(q, o, g, 0.7, m.k, m.v, ctx.row_pos, table, heads, kv_heads, hd, None, chunk,
+                                                            hd ** -0.5, ns, mws2[0], mws2[1], r1, r2, sink))
         out[f"masked_attention_decode_b{batch}"] = {"us": round(us, 1), "keys": keys, "gbs": round(moved / us / 1e3, 1),
                                                     "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
         nsplit = api.decode_splits(batch, kv_heads, heads // kv_heads, ctx.tables[f.group].shape[1])
@@ -516,7 +523,8 @@ def run_design(args):
                 ms = time_step_prefill(torch, dk, model, tokens)
                 r["prefill"][str(tokens)] = {"ms": round(ms, 3), "tok_s": round(tokens / ms * 1e3)}
             for batch in (1, 8, 64):
-                ms, launches = time_step_decode(torch, dk, model, batch, 2048, max(16, args.steps // 2), 24)
+                # 3,072 tokens of context: in the middle of a chunk of 2,048 for the chunked design (half a chunk of keys in sight)
+                ms, launches = time_step_decode(torch, dk, model, batch, 3072, max(16, args.steps // 2), 24)
                 r["decode"][f"b{batch}"] = {"ms": round(ms, 4), "tok_s": round(batch / ms * 1e3, 1), "kernels_per_step": launches,
                                             "weights_frac_hbm": round(model.weight_bytes_per_step() / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
             rec[name] = r

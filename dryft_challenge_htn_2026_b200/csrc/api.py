@@ -775,19 +775,82 @@ def attention_masked_prefill_tc(q, out, gate, out_scale, k_store, v_store, tiles
                                               c_void_p(stream)), "attention_masked_prefill_tc")
 
 
-def masked_decode_span(n_heads, n_kv_heads, head_dim, window, chunk, table_pages):
-    """The most keys a row of a decode step can see (chunk, window, or what the page table can hold), or
-    None when the scores of a kv head's query heads over that many keys do not fit a block's shared memory."""
-    span = min([x for x in (chunk, window, table_pages * PAGE) if x])
+def masked_decode_streams(q, out, gate, head_dim, v_head_dim):
+    """Whether single tokens of a masked attention run on the library's split decode kernel (its masked
+    build): keys and values of one head size in steps of 16, rows on 8-byte boundaries."""
+    if head_dim != v_head_dim or head_dim % 16 or not 16 <= head_dim <= 256:
+        return False
+    return all(t is None or (t.stride(0) % 4 == 0 and t.data_ptr() % 8 == 0) for t in (q, out, gate))
+
+
+def masked_decode_splits(n_seq, n_kv_heads, group, table_pages, window, chunk):
+    """Key splits for ``attention_decode_masked_bf16``: those of ``decode_splits`` for the pages a row can see at
+    most (its chunk or window bounds them, whatever the page table holds), never more than those pages."""
+    pages = table_pages
+    for bound in (window, chunk):
+        if bound:
+            pages = min(pages, bound // PAGE + 2)
+    return max(1, min(decode_splits(n_seq, n_kv_heads, group, pages), pages))
+
+
+def attention_decode_masked_bf16(q, out, gate, out_scale, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads,
+                                 head_dim, window, chunk, scale, nsplit, ws_acc, ws_ml, r1=None, r2=None, sink=None):
+    """``attention_decode_bf16`` in its masked build: one query token per sequence over its cached keys inside
+    its chunk and window, with the distance bias in the scores and the sink, the gate and ``out_scale`` in the
+    merge. q, gate and out may be rows of wider matrices. Scratch as ``attention_decode_ws``."""
+    _need_rows(q, "q", torch.bfloat16), _need_rows(out, "out", torch.bfloat16), _need_rows(gate, "gate", torch.bfloat16)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
+    _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
+    _need(r1, "r1", torch.float32, 1), _need(r2, "r2", torch.float32, 1), _need(sink, "sink", torch.float32, 1)
+    n_seq = q.shape[0]
+    if not 1 <= nsplit <= DECODE_MAX_SPLITS or (r1 is None) != (r2 is None) or n_heads % n_kv_heads \
+            or not masked_decode_streams(q, out, gate, head_dim, head_dim):
+        raise KernelError("attention_decode_masked_bf16: splits, head counts, head size or row strides not supported")
+    if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * 4 * nsplit * head_dim \
+            or ws_ml.numel() < n_seq * n_heads * 4 * nsplit * 2:
+        raise KernelError("attention_decode_masked_bf16: scratch too small for this batch and split count")
+    lib = _lib("attention_bf16.cu", {"HD": head_dim, "DK_MASKED": 1})
+    _check(lib, lib.dk_attn_decode_masked_bf16(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), _p(gate),
+                                               c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
+                                               _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store), _p(row_pos), _p(page_table),
+                                               page_table.shape[1], n_seq, n_heads, n_kv_heads, int(window or 0),
+                                               int(chunk or 0), c_float(scale), _p(r1), _p(r2), _p(sink), nsplit, _stream()),
+           "attention_decode_masked_bf16", 2)
+
+
+MASKED_DECODE_MAX_SPLITS = 16
+
+
+def masked_decode_span(n_heads, n_kv_heads, head_dim, window, chunk, table_pages, rows=None):
+    """(most keys a block of a decode step handles, splits of a row's keys over blocks), or None when the
+    scores of a kv head's query heads over that many keys do not fit a block's shared memory. A row sees at
+    most a chunk, a window, or what the page table can hold; its keys are split so that the blocks fill the
+    GPU about twice (fixed by the batch and the sizes, not by the sequences' lengths: a captured step replays
+    it), while a split keeps at least 128 keys."""
+    most = min([x for x in (chunk, window, table_pages * PAGE) if x])
     g = n_heads // n_kv_heads
-    return span if 4 * g * (head_dim + span) <= _MASKED_DECODE_SMEM else None
+    nsplit = 1
+    if rows:
+        nsplit = max(1, min(MASKED_DECODE_MAX_SPLITS, -(-2 * sm_count() // (rows * n_kv_heads)), most // 128))
+    span = -(-most // nsplit)
+    while 4 * g * (head_dim + span) > _MASKED_DECODE_SMEM and nsplit < MASKED_DECODE_MAX_SPLITS:
+        nsplit += 1
+        span = -(-most // nsplit)
+    return (span, nsplit) if 4 * g * (head_dim + span) <= _MASKED_DECODE_SMEM else None
+
+
+def masked_decode_ws(rows, n_heads, v_head_dim, nsplit, device):
+    """Scratch of a split attention_masked_decode_bf16: the parts' unnormalised outputs and (maximum, sum) pairs."""
+    return (torch.empty(rows * n_heads * nsplit * v_head_dim, dtype=torch.float32, device=device),
+            torch.empty(rows * n_heads * nsplit * 2, dtype=torch.float32, device=device))
 
 
 def attention_masked_decode_bf16(q, out, gate, out_scale, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads,
                                  head_dim, v_head_dim, window, chunk, scale, span, r1=None, r2=None, sink=None,
-                                 k_new=None, v_new=None):
+                                 k_new=None, v_new=None, ws=None):
     """``attention_masked`` for one query token per sequence (bfloat16 storage, float32 arithmetic): a block
-    per (kv head, row) for all query heads of the group. ``span`` from ``masked_decode_span``. With
+    per (kv head, row, run of keys) for all query heads of the group, and a merge kernel when the keys are
+    split. ``span`` = (keys a block, splits) from ``masked_decode_span``, ``ws`` from ``masked_decode_ws``. With
     ``k_new`` / ``v_new`` (rows of the step's projection) the kernel writes each token's key and value into
     the cache itself before it reads it."""
     _need_rows(k_new, "k_new", torch.bfloat16), _need_rows(v_new, "v_new", torch.bfloat16)
@@ -800,14 +863,19 @@ def attention_masked_decode_bf16(q, out, gate, out_scale, k_store, v_store, row_
     if n_heads % n_kv_heads or (r1 is None) != (r2 is None) or q.stride(0) % 2 or out.stride(0) % 2 or \
             (gate is not None and gate.stride(0) % 2):
         raise KernelError("attention_masked_decode_bf16: head counts or row strides not supported")
+    span, nsplit = span
+    if nsplit > 1 and (ws is None or ws[0].numel() < q.shape[0] * n_heads * nsplit * v_head_dim
+                       or ws[1].numel() < q.shape[0] * n_heads * nsplit * 2):
+        raise KernelError("attention_masked_decode_bf16: scratch missing or too small for this batch and split count")
     lib = _masked_lib(head_dim, v_head_dim)
     _check(lib, lib.dk_attn_masked_decode_bf16(_p(q), c_longlong(q.stride(0)), _p(out), c_longlong(out.stride(0)), _p(gate),
                                                c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
                                                _p(k_store), _p(v_store), _p(row_pos), _p(page_table), page_table.shape[1],
                                                q.shape[0], n_heads, n_kv_heads, int(window or 0), int(chunk or 0),
                                                c_float(scale), _p(r1), _p(r2), _p(sink), int(span), _p(k_new), _p(v_new),
-                                               c_longlong(k_new.stride(0) if k_new is not None else 0), _stream()),
-           "attention_masked_decode_bf16")
+                                               c_longlong(k_new.stride(0) if k_new is not None else 0), nsplit,
+                                               _p(ws[0] if nsplit > 1 else None), _p(ws[1] if nsplit > 1 else None), _stream()),
+           "attention_masked_decode_bf16", 1 if nsplit == 1 else 2)
 
 
 # ------------------------------------------------------------------------ decayed linear attention

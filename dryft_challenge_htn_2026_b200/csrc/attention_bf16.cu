@@ -10,7 +10,17 @@
 //    its own; the combine kernel merges the 4 x splits partial results of a head.
 // Prefill stages key/value pages ([64, HD] per kv head, contiguous) with cp.async, two stages deep. P is rounded to bfloat16 before P.V; row sums use the unrounded values.
 // Reference formulas: engine/fused.py:301-343 (prefill), :478-565 (split decode + combine).
+//
+// Built with -DDK_MASKED=1 the decode kernel and its merge are also the single-token attention of mixers
+// with further options (entry point dk_attn_decode_masked_bf16): a chunk mask beside the window, a
+// logarithmic distance bias with two numbers a head, a sink that joins the merged denominator, an output gate
+// and a constant factor on the merged row, and q, gate and out as rows of wider matrices. The plain build
+// has none of this code.
 #include "attention_mma.cuh"
+
+#ifndef DK_MASKED
+#define DK_MASKED 0
+#endif
 
 constexpr size_t SMEM_BYTES = 2 * STAGE_ELEMS * sizeof(bf16);
 
@@ -109,7 +119,11 @@ attn_prefill_kernel(const bf16* q, bf16* out, const bf16* k_store, const bf16* v
 template <int D>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
-                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2) {
+                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2
+#if DK_MASKED
+                   , long long ldq, int chunk, const float* __restrict__ r1, const float* __restrict__ r2
+#endif
+                   ) {
     extern __shared__ __align__(16) bf16 smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
@@ -128,7 +142,12 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
     bf16* ring = smem + warp * D * CHUNK;
     const int pos = row_pos[b];
     const int* pt = page_table + (size_t)b * pt_stride;
+#if DK_MASKED
+    int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0 && pos >= 0) key_lo = max(key_lo, pos / chunk * chunk);
+#else
     const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+#endif
     const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
     const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
     const int jt0 = t_lo + split * per, jt1 = pos >= 0 ? min(t_hi + 1, jt0 + per) : jt0;  // [jt0, jt1)
@@ -161,7 +180,19 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
 
     if (jt0 < jt1) {
         uint32_t qf[HD / 16][4];
+#if DK_MASKED
+        const bf16* qb = q + (size_t)b * ldq + (size_t)head0 * HD;
+        // rows are heads here: each has its own two numbers of the distance bias
+        float bias_rows[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r1 != nullptr) {
+            if (g < heads_here) bias_rows[0] = r1[head0 + g], bias_rows[2] = r2[head0 + g];
+            if (g + 8 < heads_here) bias_rows[1] = r1[head0 + g + 8], bias_rows[3] = r2[head0 + g + 8];
+        }
+        const float* bias = r1 != nullptr ? bias_rows : nullptr;
+#else
         const bf16* qb = q + ((size_t)b * nh + head0) * HD;
+        const float* bias = nullptr;
+#endif
         load_q_frags(qf, g < heads_here ? qb + (size_t)g * HD : nullptr,
                      g + 8 < heads_here ? qb + (size_t)(g + 8) * HD : nullptr);
         const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
@@ -172,7 +203,7 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
             const int key0 = jt * DK_PAGE + warp * 16;
             if (key0 <= pos && key0 + 15 >= key_lo) {
                 const bf16* Ks = ring + slot * CHUNK;
-                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, lo, hi, sl2, m, l, acc);
+                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, lo, hi, sl2, m, l, acc, bias);
             }
             __syncwarp();                     // every lane is done reading the slot before it is refilled
             if (jt + D < jt1) fetch(jt + D, slot);
@@ -206,7 +237,11 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
 // holds the (max, sum) of parts s, s + 32, s + 64 and s + 96; the partial outputs of the first 16
 // parts are requested together with them, so up to 16 parts cost one trip to memory after the wait.
 __global__ void __launch_bounds__(128)
-attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int parts, int n_heads) {
+attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int parts, int n_heads
+#if DK_MASKED
+                    , int nh, long long ldo, const bf16* gate, long long ldg, float out_scale, const float* __restrict__ sink
+#endif
+                    ) {
     pdl_launch_dependents();   // before the wait: see pdl_launch_dependents
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -233,6 +268,11 @@ attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int part
                 float M = fmaxf(fmaxf(pm[0].x, pm[1].x), fmaxf(pm[2].x, pm[3].x));
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+#if DK_MASKED
+                // the sink: one more term of the denominator, in the log2 domain like the parts' maxima
+                const float sink2 = sink != nullptr ? sink[head % nh] * 1.4426950408889634f : -INFINITY;
+                M = fmaxf(M, sink2);
+#endif
                 float L = 0.f;
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
@@ -241,7 +281,12 @@ attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int part
                 }
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
+#if DK_MASKED
+                if (sink != nullptr) L += exp2f(sink2 - M);
+                inv = L > 0.f ? out_scale / L : 0.f;
+#else
                 inv = L > 0.f ? 1.f / L : 0.f;
+#endif
             }
             const float fsrc = fw[s0 >> 5];         // a run of 16 parts lies in one group of 32
 #pragma unroll
@@ -252,9 +297,23 @@ attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int part
         }
         if (ok) {
             uint2 o;
+#if DK_MASKED
+            const size_t row = head / nh, col = (head % nh) * HD + d0;
+            float x[4] = {a.x * inv, a.y * inv, a.z * inv, a.w * inv};
+            if (gate != nullptr) {
+                const uint2 gk = *reinterpret_cast<const uint2*>(gate + row * ldg + col);
+                const bf16* g4 = reinterpret_cast<const bf16*>(&gk);
+#pragma unroll
+                for (int i = 0; i < 4; i++) x[i] *= 1.f / (1.f + __expf(-__bfloat162float(g4[i])));
+            }
+            o.x = pack_bf16(x[0], x[1]);
+            o.y = pack_bf16(x[2], x[3]);
+            *reinterpret_cast<uint2*>(out + row * ldo + col) = o;
+#else
             o.x = pack_bf16(a.x * inv, a.y * inv);
             o.y = pack_bf16(a.z * inv, a.w * inv);
             *reinterpret_cast<uint2*>(out + head * HD + d0) = o;
+#endif
         }
     }
 }
@@ -282,6 +341,7 @@ static int ensure_smem_attr() {
     return 0;
 }
 
+#if !DK_MASKED
 DK_EXPORT int dk_attn_head_dim() { return HD; }
 
 DK_EXPORT int dk_attn_prefill_bf16(const void* q, void* out, const void* k_store, const void* v_store, const int* tiles,
@@ -316,3 +376,31 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
     return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
                      (const float*)ws_ml, (bf16*)out, 4 * nsplit, n_seq * nh);
 }
+#else
+// As dk_attn_decode_bf16 with the options of the masked build: q, gate and out are rows of wider matrices (ldq, ldg,
+// ldo elements apart, multiples of 4, on 8-byte boundaries); gate, r1/r2 and sink may be null. Keys and values of
+// equal head size HD; the token's own key and value are in the cache when this runs.
+DK_EXPORT int dk_attn_decode_masked_bf16(const void* q, long long ldq, void* out, long long ldo, const void* gate, long long ldg,
+                                         float out_scale, float* ws_acc, float* ws_ml, const void* k_store, const void* v_store,
+                                         const int* row_pos, const int* page_table, int pt_stride, int n_seq, int nh, int nkv,
+                                         int window, int chunk, float scale, const float* r1, const float* r2,
+                                         const float* sink, int nsplit, cudaStream_t st) {
+    if (nh % nkv != 0 || nsplit < 1 || nsplit > 32 || ws_acc == nullptr || ws_ml == nullptr || ldq % 2 || ldo % 4 ||
+        (gate && ldg % 4) || ((uintptr_t)out | (uintptr_t)gate) % 8 != 0 || (uintptr_t)q % 4 != 0)
+        return (int)cudaErrorInvalidValue;
+    int e = ensure_smem_attr();
+    if (e) return e;
+    const int G = nh / nkv, mtiles = (G + 15) / 16;
+    if (decode_ring_depth((long long)nsplit * nkv * mtiles * n_seq) == 3)
+        e = dk_launch(attn_decode_kernel<3>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(3), st, (const bf16*)q,
+                      ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv,
+                      window, scale * 1.4426950408889634f, ldq, chunk, r1, r2);
+    else
+        e = dk_launch(attn_decode_kernel<2>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(2), st, (const bf16*)q,
+                      ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv,
+                      window, scale * 1.4426950408889634f, ldq, chunk, r1, r2);
+    if (e) return e;
+    return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
+                     (const float*)ws_ml, (bf16*)out, 4 * nsplit, n_seq * nh, nh, ldo, (const bf16*)gate, ldg, out_scale, sink);
+}
+#endif

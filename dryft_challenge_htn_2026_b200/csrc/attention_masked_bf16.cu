@@ -236,9 +236,10 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
                           float out_scale, const bf16* k_store, const bf16* v_store, const int* row_pos,
                           const int* page_table, int pt_stride, int nh, int nkv, int window, int chunk, float scale,
                           const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink,
-                          int span, const bf16* k_new, const bf16* v_new, long long ldkv, bf16* k_out, bf16* v_out) {
+                          int span, const bf16* k_new, const bf16* v_new, long long ldkv, bf16* k_out, bf16* v_out,
+                          int nsplit, float* ws_acc, float* ws_ml) {
     extern __shared__ __align__(16) float fsm[];
-    const int G = nh / nkv, kvh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int G = nh / nkv, kvh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, split = blockIdx.z;
     float* red = fsm;                       // [key split][4 heads][HDV]
     float* qs = fsm + MD_RED_FLOATS;        // [G][HD]
     float* sc = qs + G * HD;                // [G][span]
@@ -249,9 +250,23 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
         for (int i = tid; i < G * HDV; i += MD_THREADS) out[(size_t)b * ldo + (size_t)kvh * G * HDV + i] = __float2bfloat16_rn(0.f);
         return;
     }
-    const int lo = first_key(pos, window, chunk), n = pos - lo + 1;
+    // With nsplit > 1 the visible keys are dealt out to nsplit blocks in equal runs; each leaves its part of the
+    // softmax (maximum, sum, unnormalised P.V) for the merge kernel. The run that ends at the token's own position
+    // belongs to the block that also stores the token's key and value.
+    const int lo_all = first_key(pos, window, chunk), n_all = pos - lo_all + 1;
+    const int per = (n_all + nsplit - 1) / nsplit;
+    const int lo = lo_all + split * per, n = max(0, min(per, n_all - split * per));
     const int* pt = page_table + (size_t)b * pt_stride;
-    if (k_new != nullptr) {   // the token's own key and value go into the cache here, by the block that reads them first
+    if (nsplit > 1 && n == 0) {                   // nothing for this block: a part that counts for nothing
+        for (int i = tid; i < G; i += MD_THREADS) {
+            float* ml = ws_ml + (((size_t)b * nh + kvh * G + i) * nsplit + split) * 2;
+            ml[0] = -INFINITY, ml[1] = 0.f;
+        }
+        for (int i = tid; i < G * HDV; i += MD_THREADS)
+            ws_acc[(((size_t)b * nh + kvh * G + i / HDV) * nsplit + split) * HDV + i % HDV] = 0.f;
+        return;
+    }
+    if (k_new != nullptr && lo + n - 1 == pos) {   // the token's own key and value go into the cache here, by the block that reads them
         const int page = pt[pos / DK_PAGE];
         for (int i = tid; i < HD; i += MD_THREADS)
             k_out[kv_offset(page, nkv, kvh, pos % DK_PAGE, HD) + i] = k_new[(size_t)b * ldkv + (size_t)kvh * HD + i];
@@ -295,7 +310,7 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
     const int lane = tid & 31, warp = tid >> 5;
     for (int gq = warp; gq < G; gq += MD_THREADS / 32) {
         const int h = kvh * G + gq;
-        float mx = sink ? sink[h] : -INFINITY;
+        float mx = (sink && nsplit == 1) ? sink[h] : -INFINITY;
         for (int jj = lane; jj < n; jj += 32) mx = fmaxf(mx, sc[gq * span + jj]);
         mx = warp_max(mx);
         float sum = 0.f;
@@ -305,6 +320,13 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
             sum += p;
         }
         sum = warp_sum(sum);
+        if (nsplit > 1) {                         // the part's maximum and sum; its weights stay unnormalised
+            if (lane == 0) {
+                float* ml = ws_ml + (((size_t)b * nh + h) * nsplit + split) * 2;
+                ml[0] = mx, ml[1] = sum;
+            }
+            continue;
+        }
         if (sink) sum += expf(sink[h] - mx);
         const float inv = out_scale / sum;
         for (int jj = lane; jj < n; jj += 32) sc[gq * span + jj] *= inv;
@@ -350,10 +372,46 @@ attn_masked_decode_kernel(const bf16* q, long long ldq, bf16* out, long long ldo
             float a = 0.f;
             for (int kk = 0; kk < KS; kk++) a += red[(kk * 4 + gg) * HDV + d];
             const size_t col = (size_t)(kvh * G + g0 + gg) * HDV + d;
+            if (nsplit > 1) {
+                ws_acc[(((size_t)b * nh + kvh * G + g0 + gg) * nsplit + split) * HDV + d] = a;
+                continue;
+            }
             if (gate) a *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)b * ldg + col])));
             out[(size_t)b * ldo + col] = __float2bfloat16_rn(a);
         }
         __syncthreads();
+    }
+}
+
+// The parts of a split single-token attention put together: a warp per (row, head). M = max(sink, the parts'
+// maxima), L = e^(sink - M) + sum_s l_s e^(m_s - M), out = sum_s acc_s e^(m_s - M) / L * sigmoid(gate) * out_scale.
+__global__ void attn_masked_merge_kernel(const float* ws_acc, const float* ws_ml, bf16* out, long long ldo, const bf16* gate,
+                                         long long ldg, float out_scale, const float* __restrict__ sink, const int* row_pos,
+                                         int n_rows, int nh, int nsplit) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= n_rows * nh) return;
+    const int b = wid / nh, h = wid % nh;
+    bf16* o = out + (size_t)b * ldo + (size_t)h * HDV;
+    if (row_pos[b] < 0) {
+        for (int d = lane; d < HDV; d += 32) o[d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const float* ml = ws_ml + ((size_t)b * nh + h) * nsplit * 2;
+    const float* acc = ws_acc + ((size_t)b * nh + h) * nsplit * HDV;
+    float M = sink ? sink[h] : -INFINITY;
+    for (int s = 0; s < nsplit; s++) M = fmaxf(M, ml[2 * s]);
+    float L = sink ? expf(sink[h] - M) : 0.f;
+    for (int s = 0; s < nsplit; s++) L += ml[2 * s + 1] * expf(ml[2 * s] - M);
+    const float inv = out_scale / L;
+    for (int d = lane; d < HDV; d += 32) {
+        float a = 0.f;
+        for (int s = 0; s < nsplit; s++) a = fmaf(acc[(size_t)s * HDV + d], expf(ml[2 * s] - M), a);
+        a *= inv;
+        if (gate) a *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)b * ldg + (size_t)h * HDV + d])));
+        o[d] = __float2bfloat16_rn(a);
     }
 }
 
@@ -377,14 +435,16 @@ DK_EXPORT int dk_attn_masked_prefill_bf16(const void* q, long long ldq, void* ou
 
 // k_new, v_new (or null): rows [n_rows, nkv*HD] / [n_rows, nkv*HDV] of the step's projection, ldkv elements apart,
 // which the kernel stores at each row's position before it reads the cache (no separate cache-write launch).
+// nsplit > 1: the keys of a row in nsplit runs, a block each, then the merge kernel; ws_acc [rows, nh, nsplit, HDV]
+// and ws_ml [rows, nh, nsplit, 2] float32 scratch; span is then the most keys of a run.
 // span: the most keys any row sees (the chunk, the window, or the longest sequence's length, rounded up by the caller)
 DK_EXPORT int dk_attn_masked_decode_bf16(const void* q, long long ldq, void* out, long long ldo, const void* gate,
                                          long long ldg, float out_scale, const void* k_store, const void* v_store,
                                          const int* row_pos, const int* page_table, int pt_stride, int n_rows, int nh,
                                          int nkv, int window, int chunk, float scale, const float* r1, const float* r2,
                                          const float* sink, int span, const void* k_new, const void* v_new, long long ldkv,
-                                         cudaStream_t st) {
-    if (nh % nkv != 0) return (int)cudaErrorInvalidValue;
+                                         int nsplit, float* ws_acc, float* ws_ml, cudaStream_t st) {
+    if (nh % nkv != 0 || nsplit < 1 || (nsplit > 1 && (ws_acc == nullptr || ws_ml == nullptr))) return (int)cudaErrorInvalidValue;
     const int G = nh / nkv;
     const size_t smem = sizeof(float) * ((size_t)MD_RED_FLOATS + (size_t)G * HD + (size_t)G * span);
     if (smem > 224 * 1024) return (int)cudaErrorInvalidValue;
@@ -393,8 +453,11 @@ DK_EXPORT int dk_attn_masked_decode_bf16(const void* q, long long ldq, void* out
         cudaFuncSetAttribute(attn_masked_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr = smem;
     }
-    return dk_launch(attn_masked_decode_kernel, dim3(nkv, n_rows), dim3(MD_THREADS), smem, st, (const bf16*)q, ldq, (bf16*)out,
-                     ldo, (const bf16*)gate, ldg, out_scale, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table,
-                     pt_stride, nh, nkv, window, chunk, scale, r1, r2, sink, span, (const bf16*)k_new, (const bf16*)v_new, ldkv,
-                     (bf16*)k_store, (bf16*)v_store);
+    int e = dk_launch(attn_masked_decode_kernel, dim3(nkv, n_rows, nsplit), dim3(MD_THREADS), smem, st, (const bf16*)q, ldq,
+                      (bf16*)out, ldo, (const bf16*)gate, ldg, out_scale, (const bf16*)k_store, (const bf16*)v_store, row_pos,
+                      page_table, pt_stride, nh, nkv, window, chunk, scale, r1, r2, sink, span, (const bf16*)k_new,
+                      (const bf16*)v_new, ldkv, (bf16*)k_store, (bf16*)v_store, nsplit, ws_acc, ws_ml);
+    if (e != 0 || nsplit == 1) return e;
+    return dk_launch(attn_masked_merge_kernel, dim3((n_rows * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
+                     (const float*)ws_ml, (bf16*)out, ldo, (const bf16*)gate, ldg, out_scale, sink, row_pos, n_rows, nh, nsplit);
 }

@@ -62,11 +62,12 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[HD / 16][4], const b
 
 // One warp: 16 query rows against NKEYS staged keys (rows of Ks / Vs), online softmax update.
 // Row r (0: lane group g, 1: g+8) may see keys with lo[r] <= absolute position <= hi[r].
-// Scores are kept in the log2 domain: sl2 = scale * log2(e).
+// Scores are kept in the log2 domain: sl2 = scale * log2(e). ``bias`` (or null) = {b1 of row 0, b1 of row 1, b2 of
+// row 0, b2 of row 1}: a logarithmic distance bias b1 * log2(1 + b2 * (hi[r] - key)) is taken off row r's scores.
 template <int NKEYS>
 __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[HD / 16][4], const bf16* Ks, const bf16* Vs, int key0,
                                             const int (&lo)[2], const int (&hi)[2], float sl2, float (&m)[2],
-                                            float (&l)[2], float (&acc)[HD / 8][4]) {
+                                            float (&l)[2], float (&acc)[HD / 8][4], const float* bias = nullptr) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NKEYS / 8][4];
 #pragma unroll
@@ -88,7 +89,11 @@ __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[HD / 16][4], co
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             const int key = key0 + nt * 8 + 2 * t + (c & 1), r = c >> 1;
-            const float v = (key >= lo[r] && key <= hi[r]) ? s[nt][c] * sl2 : -INFINITY;
+            float v = -INFINITY;
+            if (key >= lo[r] && key <= hi[r]) {
+                v = s[nt][c] * sl2;
+                if (bias != nullptr) v -= bias[r] * __log2f(fmaf(bias[2 + r], (float)(hi[r] - key), 1.f));
+            }
             s[nt][c] = v;
             mx[r] = fmaxf(mx[r], v);
         }

@@ -128,6 +128,7 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
     jobs += [("attention_bf16.cu", {"HD": hd}) for hd in head_dims]
     jobs += [("attention_tc.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]
     jobs += [("attention_tc.cu", {"HD": hd, "DK_MASKED": 1}) for hd in head_dims if hd in (64, 128)]
+    jobs += [("attention_bf16.cu", {"HD": hd, "DK_MASKED": 1}) for hd in head_dims if hd in (64, 128)]
     jobs += [("attention_masked_bf16.cu", {"HD": hd, "HDV": hd}) for hd in head_dims if hd in (64, 128)]
     jobs += [("linear_attention_bf16.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:

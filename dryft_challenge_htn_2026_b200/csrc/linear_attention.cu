@@ -15,37 +15,40 @@
 
 __device__ __forceinline__ float act_silu(float x) { return x / (1.f + expf(-x)); }
 
-// Block (sequence s, head h). Thread (rg, c): column c of the state, rows rg, rg + R, ... (R row groups).
+// Block (sequence s, head h, slice of up to cslice value columns: the columns of a state evolve independently,
+// and a slice of 32 keeps a thread's share of the state at hd / 8 registers, so that several blocks fit an
+// SM). Thread (rg, c): column c of the slice, rows rg, rg + R, ... (R row groups).
 // cu_q == nullptr: one token per sequence (row s is sequence s). seq_pos0[s] < 0: a padding row.
 template <typename T, int EPT>
 __global__ void __launch_bounds__(LA_THREADS)
 linear_attention_step_kernel(const T* q, const T* k, const T* v, long long ld, float* out, float* state,
                              const int* cu_q, const int* seq_pos0, const int* seq_slot, const float* __restrict__ decay,
-                             int nh, int hd, int hdv, int cols_pad) {
+                             int nh, int hd, int hdv, int cols_pad, int cslice) {
     extern __shared__ float sm[];
     const int R = LA_THREADS / cols_pad;
     float* sq = sm;                              // [LA_TB][hd]
     float* sk = sq + LA_TB * hd;                 // [LA_TB][hd]
-    float* sv = sk + LA_TB * hd;                 // [LA_TB][hdv]
-    float* part = sv + LA_TB * hdv;              // [LA_TB][R][cols_pad]
+    float* sv = sk + LA_TB * hd;                 // [LA_TB][cslice]
+    float* part = sv + LA_TB * cslice;           // [LA_TB][R][cols_pad]
     pdl_wait();
     pdl_launch_dependents();
-    const int s = blockIdx.x, h = blockIdx.y;
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cslice;
+    const int cols = min(cslice, hdv - col0);            // value columns of this block: [col0, col0 + cols)
     const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
     const int tid = threadIdx.x, c = tid % cols_pad, rg = tid / cols_pad;
     const size_t ow = (size_t)nh * hdv;
     if (seq_pos0[s] < 0) {
         for (int t = r0; t < r1; t++)
-            for (int i = tid; i < hdv; i += LA_THREADS) out[(size_t)t * ow + (size_t)h * hdv + i] = 0.f;
+            for (int i = tid; i < cols; i += LA_THREADS) out[(size_t)t * ow + (size_t)h * hdv + col0 + i] = 0.f;
         return;
     }
     const float d = decay[h];
-    float* S = state + ((size_t)seq_slot[s] * nh + h) * (size_t)hd * hdv;
+    float* S = state + ((size_t)seq_slot[s] * nh + h) * (size_t)hd * hdv + col0;
     float st[EPT];
 #pragma unroll
     for (int i = 0; i < EPT; i++) {
         const int row = rg + R * i;
-        st[i] = (row < hd && c < hdv) ? S[(size_t)row * hdv + c] : 0.f;
+        st[i] = (row < hd && c < cols) ? S[(size_t)row * hdv + c] : 0.f;
     }
     for (int t0 = r0; t0 < r1; t0 += LA_TB) {
         const int nt = min(LA_TB, r1 - t0);
@@ -55,11 +58,11 @@ linear_attention_step_kernel(const T* q, const T* k, const T* v, long long ld, f
             sq[i] = act_silu(to_f(q[at]));
             sk[i] = act_silu(to_f(k[at]));
         }
-        for (int i = tid; i < nt * hdv; i += LA_THREADS)
-            sv[i] = act_silu(to_f(v[(size_t)(t0 + i / hdv) * ld + (size_t)h * hdv + i % hdv]));
+        for (int i = tid; i < nt * cols; i += LA_THREADS)
+            sv[i] = act_silu(to_f(v[(size_t)(t0 + i / cols) * ld + (size_t)h * hdv + col0 + i % cols]));
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            const float vc = c < hdv ? sv[tt * hdv + c] : 0.f;
+            const float vc = c < cols ? sv[tt * cols + c] : 0.f;
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < EPT; i++) {
@@ -72,17 +75,17 @@ linear_attention_step_kernel(const T* q, const T* k, const T* v, long long ld, f
             part[(tt * R + rg) * cols_pad + c] = o;
         }
         __syncthreads();
-        for (int i = tid; i < nt * hdv; i += LA_THREADS) {
-            const int tt = i / hdv, cc = i % hdv;
+        for (int i = tid; i < nt * cols; i += LA_THREADS) {
+            const int tt = i / cols, cc = i % cols;
             float o = 0.f;
             for (int g = 0; g < R; g++) o += part[(tt * R + g) * cols_pad + cc];
-            out[(size_t)(t0 + tt) * ow + (size_t)h * hdv + cc] = o;
+            out[(size_t)(t0 + tt) * ow + (size_t)h * hdv + col0 + cc] = o;
         }
     }
 #pragma unroll
     for (int i = 0; i < EPT; i++) {
         const int row = rg + R * i;
-        if (row < hd && c < hdv) S[(size_t)row * hdv + c] = st[i];
+        if (row < hd && c < cols) S[(size_t)row * hdv + c] = st[i];
     }
 }
 
@@ -110,18 +113,19 @@ template <typename T>
 static int launch_step(const void* q, const void* k, const void* v, long long ld, float* out, float* state,
                        const int* cu_q, const int* seq_pos0, const int* seq_slot, const float* decay, int n_seq, int nh,
                        int hd, int hdv, cudaStream_t st) {
+    const int cslice = hdv < 32 ? hdv : 32;
     int cols_pad = 1;
-    while (cols_pad < hdv) cols_pad <<= 1;
+    while (cols_pad < cslice) cols_pad <<= 1;
     const int R = LA_THREADS / cols_pad;
     const int ept = (hd + R - 1) / R;
-    const size_t smem = sizeof(float) * (size_t)(LA_TB * (2 * hd + hdv) + LA_TB * LA_THREADS);
-    const dim3 grid(n_seq, nh), block(LA_THREADS);
+    const size_t smem = sizeof(float) * (size_t)(LA_TB * (2 * hd + cslice) + LA_TB * LA_THREADS);
+    const dim3 grid(n_seq, nh, (hdv + cslice - 1) / cslice), block(LA_THREADS);
 #define LA_STEP(E)                                                                                                       \
     if (ept <= E) {                                                                                                      \
         if (smem > 48 * 1024)                                                                                            \
             cudaFuncSetAttribute(linear_attention_step_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return dk_launch(linear_attention_step_kernel<T, E>, grid, block, smem, st, (const T*)q, (const T*)k, (const T*)v, \
-                         ld, out, state, cu_q, seq_pos0, seq_slot, decay, nh, hd, hdv, cols_pad);                         \
+                         ld, out, state, cu_q, seq_pos0, seq_slot, decay, nh, hd, hdv, cols_pad, cslice);                 \
     }
     LA_STEP(4) LA_STEP(8) LA_STEP(16) LA_STEP(32) LA_STEP(64) LA_STEP(128) LA_STEP(256)
 #undef LA_STEP

@@ -89,11 +89,26 @@ class MaskedAttention(Part):
         v = proj[:, self.n_q + self.n_k:self.n_q + self.n_k + self.n_v]
         gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
-        span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1]) \
+        if self.tensor_core and ctx.is_decode and api.masked_decode_streams(q, mid, gate, s.head_dim, s.v_head_dim):
+            # single tokens, keys and values of one size: the library's split decode kernel in its masked build
+            if writes:
+                api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
+            nsplit = api.masked_decode_splits(ctx.n_seq, s.num_kv_heads, s.num_heads // s.num_kv_heads, table.shape[1],
+                                              s.window, s.chunk)
+            ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, s.num_heads, s.head_dim, nsplit),
+                                        lambda: api.attention_decode_ws(ctx.n_seq, s.num_heads, s.head_dim, nsplit, self.rt.device))
+            return api.attention_decode_masked_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, table, s.num_heads,
+                                                    s.num_kv_heads, s.head_dim, s.window, s.chunk, s.scale, nsplit, ws_acc,
+                                                    ws_ml, self.r1, self.r2, self.sink)
+        span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1], ctx.n_tok) \
             if self.tensor_core and ctx.is_decode else None
         if span is not None:      # single tokens: the kernel stores each token's key and value itself
+            ws = None
+            if span[1] > 1:
+                ws = ctx.scratch(("masked_decode", ctx.n_tok, s.num_heads, s.v_head_dim, span[1]),
+                                 lambda: api.masked_decode_ws(ctx.n_tok, s.num_heads, s.v_head_dim, span[1], self.rt.device))
             return api.attention_masked_decode_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, table, *sizes, span,
-                                                    self.r1, self.r2, self.sink, k if writes else None, v if writes else None)
+                                                    self.r1, self.r2, self.sink, k if writes else None, v if writes else None, ws)
         if writes:
             api.kv_write(k, v, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, s.num_kv_heads, s.head_dim, s.v_head_dim)
         if self.tc_tiles is not None and not ctx.is_decode and api.masked_tc_takes(q, mid, gate, s.head_dim, s.v_head_dim):
