@@ -32,9 +32,6 @@ class MaskedAttention(Part):
         self.n_q, self.n_k = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         self.n_v, self.n_mid = s.num_kv_heads * s.v_head_dim, s.num_heads * s.v_head_dim
         self.n_in = self.n_q + self.n_k + self.n_v + (self.n_mid if s.output_gate else 0)
-        if rt.dtype == torch.bfloat16 and (s.hidden_size % 8 or self.n_mid % 8):
-            raise ValueError("bfloat16 projections need inner sizes that are multiples of 8, not "
-                             f"{s.hidden_size} / {self.n_mid}")
         self.r1 = self.r2 = self.sink = None
         # the tensor-core kernels take bfloat16 with head sizes in steps of 16; everything else (float32, odd
         # head sizes) runs on the float32-arithmetic kernel, which serves every phase
@@ -101,7 +98,7 @@ class MaskedAttention(Part):
                                                     s.num_kv_heads, s.head_dim, s.window, s.chunk, s.scale, nsplit, ws_acc,
                                                     ws_ml, self.r1, self.r2, self.sink)
         span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1], ctx.n_tok) \
-            if self.tensor_core and ctx.is_decode else None
+            if self.tensor_core and ctx.is_decode and all(t is None or t.stride(0) % 2 == 0 for t in (q, mid, gate)) else None
         if span is not None:      # single tokens: the kernel stores each token's key and value itself
             ws = None
             if span[1] > 1:
@@ -115,7 +112,8 @@ class MaskedAttention(Part):
             return api.attention_masked_prefill_tc(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tc_tiles.key], ctx.cu_q,
                                                    ctx.seq_pos0, table, s.num_heads, s.num_kv_heads, s.head_dim, s.window,
                                                    s.chunk, s.scale, self.r1, self.r2, self.sink)
-        if self.tensor_core and not ctx.is_decode:
+        even = all(t is None or (t.stride(0) % 2 == 0 and t.data_ptr() % 4 == 0) for t in (q, mid, gate))
+        if self.tensor_core and not ctx.is_decode and even:
             return api.attention_masked_prefill_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tiles.key], ctx.cu_q,
                                                      ctx.seq_pos0, table, *sizes, self.r1, self.r2, self.sink)
         api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, *sizes, self.r1, self.r2,

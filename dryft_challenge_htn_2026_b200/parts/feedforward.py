@@ -49,9 +49,6 @@ class DenseMLP(Part):
         super().__init__(spec, rt)
         if spec.activation != "xielu":
             raise ValueError(f"activation {spec.activation!r} is not implemented (xielu only)")
-        if rt.dtype == torch.bfloat16 and (spec.hidden_size % 8 or spec.intermediate_size % 8):
-            raise ValueError("bfloat16 products need hidden and intermediate sizes that are multiples of 8, "
-                             f"not {spec.hidden_size} / {spec.intermediate_size}")
 
     def param_decls(self):
         s = self.spec

@@ -26,6 +26,19 @@ def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         api.sgemm(x, w, out, mode, act)
         return out
+    if K % 8:
+        # an inner size the tensor-core kernels do not take (their rows sit on 16-byte boundaries): the library's
+        # product, and the activation as a row kernel behind it
+        if mode == STORE_F32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        out = torch.mm(x, w.t())
+        if mode == SILU:
+            half = torch.empty((M, N), dtype=x.dtype, device=x.device)
+            api.silu_mul(out, half)
+            return half
+        if mode == XIELU:
+            api.xielu(out, out, act[0], act[1])
+        return out
     if M <= api.STREAM_BEST_ROWS and K % 16 == 0:
         plan = api.stream_plan(M, N, K, mode, allow_partial)
         if plan is not None:

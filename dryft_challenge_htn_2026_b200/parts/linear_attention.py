@@ -24,9 +24,6 @@ class LinearAttention(Part):
             raise ValueError(f"linear attention takes head sizes up to 256, not {s.head_dim} / {s.v_head_dim}")
         self.n_qk, self.n_mid = s.num_heads * s.head_dim, s.num_heads * s.v_head_dim
         self.n_in = 2 * self.n_qk + self.n_mid + (self.n_mid if s.output_gate else 0)
-        if rt.dtype == torch.bfloat16 and (s.hidden_size % 8 or self.n_mid % 8):
-            raise ValueError("bfloat16 projections need inner sizes that are multiples of 8, not "
-                             f"{s.hidden_size} / {self.n_mid}")
         self.decay = torch.tensor(s.decay, dtype=torch.float64).to(torch.float32).to(rt.device)
         self.norm_weight = None
 

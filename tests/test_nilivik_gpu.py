@@ -4,22 +4,19 @@ decode state and the entry point. The shapes differ in every size and option: ke
 key and value heads of different sizes, chunks that are and are not whole pages, head sizes that the
 tensor-core kernels take and ones they do not, a loop that starts after the first layer, no loop at all,
 a layer without a feed-forward, a pass count of 1 to 3."""
-import math
-
 import numpy as np
 import pytest
 import torch
 
 import dryft_challenge_htn_2026_b200 as dk
 import plain_nilivik as plain
-from dryft_challenge_htn_2026_b200.cache import Cache, KVRequest, StateRequest
-from dryft_challenge_htn_2026_b200.config.specs import (DenseMLPSpec, LinearAttentionSpec, MaskedAttentionSpec,
-                                                        RMSNormSpec, ScalarRMSNormSpec, SinusoidSpec)
+from dryft_challenge_htn_2026_b200.cache import Cache, StateRequest
+from dryft_challenge_htn_2026_b200.config.specs import DenseMLPSpec, MaskedAttentionSpec, ScalarRMSNormSpec, SinusoidSpec
 from dryft_challenge_htn_2026_b200.csrc import api
 from dryft_challenge_htn_2026_b200.engine import DecodeLoop, Runner, load_model
 from dryft_challenge_htn_2026_b200.engine.batch import build_context
 from dryft_challenge_htn_2026_b200.parts import Runtime, build_part
-from helpers import random_tokens, run_trace
+from helpers import random_tokens
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda")
@@ -52,6 +49,11 @@ SHAPES = {
               loop={"start": 0, "stop": 1, "times": 2},
               layers=[layer_cfg(2, 1, 64, 64, 100, 2, 64, 64, [0.7, 0.995], 192),
                       layer_cfg(2, 2, 128, 64, 130, 1, 128, 128, [0.98], 160)]),
+    # head sizes that no tensor-core kernel takes (20, 10, 24, 12) and an inner size of the output projection (42) and
+    # of the feed-forward (52) that is no multiple of 8: the float32-arithmetic kernels and the library's product
+    "S": dict(architecture="Nilivik", vocab=136, width=48, embedding={"scale": 2.0}, norm={"eps": 1e-5}, logit_softcap=6.0,
+              loop={"start": 0, "stop": 2, "times": 2},
+              layers=[layer_cfg(3, 1, 20, 10, 50, 1, 24, 12, [0.96], 52), layer_cfg(3, 3, 20, 10, 33, 1, 24, 12, [0.8], None)]),
 }
 
 
@@ -122,9 +124,9 @@ def test_xielu_feed_forward(dtype):
 
 
 def attention_case(dtype, H, G, D, Dv, chunk, window, lens_steps, bias=True, sink=True, gate=True, plant=None, seed=0):
-    """Runs api.kv_write + api.attention_masked over one sequence cut into the steps ``lens_steps`` (and a
-    second sequence beside it, so that rows of two sequences share a step) and compares every row with
-    the plain attention over the whole sequence. ``plant`` = (query position, key position, strength):
+    """Runs the masked-attention part's ``mix`` (the cache write and whichever attention kernel the part picks for
+    the step) over one sequence cut into the steps ``lens_steps`` (and a second sequence beside it, so that rows
+    of two sequences share a step) and compares every row with the plain attention over the whole sequence. ``plant`` = (query position, key position, strength):
     that key is made the query's direction, so that its score stands out among all others."""
     T = sum(lens_steps)
     q, k, v = rnd(T, H, D, seed=seed), rnd(T, G, D, seed=seed + 1), rnd(T, G, Dv, seed=seed + 2)
@@ -277,7 +279,7 @@ def plain_logits(folder, tokens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_whole_prompts_portions_batches_and_reused_slots(tmp_path, name, dtype):
     folder, cfg = make_model(tmp_path, name)
     model = load_model(folder, dtype)
