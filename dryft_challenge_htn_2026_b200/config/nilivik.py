@@ -40,6 +40,7 @@ class NilivikConfig(ModelConfig):
     loop_stop: int
     loop_times: int
     layers: tuple = field(default=())          # the config's layer entries, checked, as plain dicts
+    loop_given: bool = True                    # config.json has a 'loop' section (then the model has its 'loop.step' table)
 
     architecture = "Nilivik"
 
@@ -97,7 +98,7 @@ class NilivikConfig(ModelConfig):
                    embedding_scale=get(emb, "scale", float, 1.0),
                    norm_eps=get(_section(d, "norm", "the"), "eps", float, positive=True),
                    logit_softcap=get(d, "logit_softcap", float, 0.0), loop_start=start, loop_stop=stop, loop_times=times,
-                   layers=tuple(_freeze(l) for l in checked))
+                   layers=tuple(_freeze(l) for l in checked), loop_given=loop is not None)
 
     def layer_dicts(self):
         return [_thaw(l) for l in self.layers]
@@ -108,7 +109,7 @@ class NilivikConfig(ModelConfig):
              "layers": self.layer_dicts()}
         if self.logit_softcap:
             d["logit_softcap"] = self.logit_softcap
-        if self.loop_stop > self.loop_start:
+        if self.loop_given:
             d["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
         return d
 
@@ -140,7 +141,6 @@ class NilivikConfig(ModelConfig):
             names = (("norm_in", "norm1"), ("mixer", "mix.")) + ((("norm_post", "norm2"), ("feed_forward", "mlp.")) if ff else ())
             layers.append(LayerSpec(prefix=f"l{i}.", norm_in=ScalarRMSNormSpec(W, eps), mixer=mixer,
                                     norm_post=ScalarRMSNormSpec(W, eps) if ff else None, feed_forward=ff, names=names))
-        looped = self.loop_stop > self.loop_start
         schedule = tuple(ScheduleEntry(layer=i, cache=k, writes=True, add_embedding=p is not None and p > 0,
                                        add_row=(LOOP_TABLE, p) if p is not None else None)
                          for k, (i, p) in enumerate(self.runs()))
@@ -149,7 +149,7 @@ class NilivikConfig(ModelConfig):
                          max_positions=1 << 20, embed_name="embed", final_norm_prefix="final.norm", head_name="head",
                          embed_scale=self.embedding_scale, embed_position=SinusoidSpec(W, SINUSOID_BASE),
                          logit_cap=self.logit_softcap or None,
-                         tables=((LOOP_TABLE, (self.loop_times, W)),) if looped else ())
+                         tables=((LOOP_TABLE, (self.loop_times, W)),) if self.loop_given else ())
 
 
 def _freeze(x):

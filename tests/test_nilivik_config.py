@@ -49,6 +49,11 @@ def test_loop_becomes_schedule_entries_with_a_cache_each():
     once = dict(BASE, loop={"start": 0, "stop": 4, "times": 1})
     spec = dk.config_from_dict(once).to_spec()
     assert [(e.layer, e.add_embedding, e.add_row) for e in spec.schedule][0] == (0, False, ("loop.step", 0))
+    empty = dict(BASE, loop={"start": 2, "stop": 2, "times": 3})      # a span without layers: nothing loops, the table is still the model's
+    cfg = dk.config_from_dict(empty)
+    spec = cfg.to_spec()
+    assert [e.layer for e in spec.schedule] == [0, 1, 2, 3] and not any(e.add_row or e.add_embedding for e in spec.schedule)
+    assert spec.tables == (("loop.step", (3, 32)),) and dk.config_from_dict(cfg.to_dict()) == cfg
 
 
 def test_spec_carries_every_constant():
