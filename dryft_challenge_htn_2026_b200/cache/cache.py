@@ -77,7 +77,7 @@ class KVGroup:
         if c is not None:
             first_needed = max(first_needed, length // c * c)
         have = self.pages[slot]
-        i = self.first[slot]
+        i = max(self.first[slot], (self.request.keep_first + PAGE - 1) // PAGE)   # the kept first positions' pages stay
         while i < len(have) and i * PAGE + PAGE - 1 < first_needed:
             self.pool.free([have[i]])
             have[i] = -1

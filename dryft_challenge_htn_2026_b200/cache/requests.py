@@ -11,13 +11,16 @@ class KVRequest:
     that is given and differs: the two then live in stores of their own). ``window``: only the last
     ``window`` tokens are ever read, older pages may be given back; None: all tokens are kept.
     ``chunk``: a token reads only keys of its own chunk of that many positions (counted from the
-    sequence's start), so pages wholly before the chunk of the next token may be given back."""
+    sequence's start), so pages wholly before the chunk of the next token may be given back.
+    ``keep_first``: the first that many positions stay in sight whatever the window or chunk: their pages
+    are never given back."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int]
     dtype: torch.dtype
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

@@ -1,12 +1,14 @@
 """Typed configuration: part specifications, the model specification built from them, and the
 architecture's own config.json reader."""
-from .specs import (AttentionSpec, DenseMLPSpec, GatedMLPSpec, LayerSpec, LinearAttentionSpec, MaskedAttentionSpec,
-                    ModelSpec, ParallelMixerSpec, RMSNormSpec, RotaryHalfSpec, ScalarRMSNormSpec, ScheduleEntry,
-                    SinusoidSpec)
+from .specs import (AttentionSpec, DenseMLPSpec, GatedLinearAttentionSpec, GatedMLPSpec, LayerSpec, LinearAttentionSpec,
+                    MaskedAttentionSpec, ModelSpec, OnePlusRMSNormSpec, ParallelMixerSpec, PostNormLayerSpec, RMSNormSpec,
+                    RotaryHalfSpec, RotaryPartSpec, RoutedMLPSpec, ScalarRMSNormSpec, ScheduleEntry, SinusoidSpec)
 from .base import ConfigError, ModelConfig
 from .nilivik import NilivikConfig
+from .pibulix import PibulixConfig
 from .qwen3 import Qwen3Config
 
 __all__ = ["AttentionSpec", "DenseMLPSpec", "GatedMLPSpec", "LayerSpec", "LinearAttentionSpec", "MaskedAttentionSpec",
            "ModelSpec", "ParallelMixerSpec", "RMSNormSpec", "RotaryHalfSpec", "ScalarRMSNormSpec", "ScheduleEntry",
-           "SinusoidSpec", "ConfigError", "ModelConfig", "NilivikConfig", "Qwen3Config"]
+           "SinusoidSpec", "ConfigError", "ModelConfig", "NilivikConfig", "Qwen3Config", "PibulixConfig",
+           "GatedLinearAttentionSpec", "OnePlusRMSNormSpec", "PostNormLayerSpec", "RotaryPartSpec", "RoutedMLPSpec"]

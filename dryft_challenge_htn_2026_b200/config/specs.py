@@ -25,6 +25,13 @@ class ScalarRMSNormSpec:
 
 
 @dataclass(frozen=True)
+class OnePlusRMSNormSpec:
+    """y = (1 + w) * x * rsqrt(mean(x^2) + eps): an RMS norm whose stored weight sits around zero."""
+    dim: int
+    eps: float
+
+
+@dataclass(frozen=True)
 class SinusoidSpec:
     """Absolute position vector added to the embedding: entry 2i = sin(p * base^(-2i/dim)), entry
     2i+1 = cos of the same angle."""
@@ -37,6 +44,15 @@ class RotaryHalfSpec:
     """Rotate-half rotary encoding over the whole head: angle(p, j) = p * theta^(-2j/dim)."""
     dim: int
     theta: float
+
+
+@dataclass(frozen=True)
+class RotaryPartSpec:
+    """Rotate-half rotation of the first ``dim`` coordinates of a head (coordinate i with i + dim/2, i below
+    dim/2) by angle(p, i) = p * base^(-2i/dim); the head's other coordinates pass. The frequencies are made in
+    float64 and rounded to float32 once; the angle is their float32 product with the position."""
+    dim: int
+    base: float
 
 
 @dataclass(frozen=True)
@@ -59,7 +75,14 @@ class MaskedAttentionSpec:
     chunks counted from the sequence's first position) and/or a sliding window; a logarithmic distance
     bias taken off the score, r1_h * ln(1 + r2_h * (i - j)), with two learned numbers a head; a sink (a
     learned number a head whose exponential joins the softmax's denominator and nothing else); an
-    output gate sigmoid(W_g x) on the concatenated heads before the output projection."""
+    output gate sigmoid(W_g x) on the concatenated heads before the output projection.
+    Further options: ``keep_first`` (the first that many positions of a sequence stay in sight of every later
+    query when the window has moved on, at their true positions); ``softcap`` (score <- cap * tanh(score /
+    cap), after the scale and before the masks); ``unit_sink`` (a sink fixed at score 0, so the softmax's
+    denominator is one plus the sum; no tensor); and what may stand between the projection and the cache:
+    ``conv_taps`` (a causal convolution over time of that many taps on every channel of q, k and v, tensors
+    ``<q|k|v>.conv`` [channels, taps], its memory a per-sequence state), ``qk_norm`` (a norm spec over
+    head_dim for q and k heads, tensors ``q.norm`` / ``k.norm``) and ``position`` (a ``RotaryPartSpec``)."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -71,6 +94,12 @@ class MaskedAttentionSpec:
     distance_bias: bool = False
     sink: bool = False
     output_gate: bool = False
+    keep_first: int = 0
+    softcap: Optional[float] = None
+    unit_sink: bool = False
+    conv_taps: Optional[int] = None
+    qk_norm: Optional[Any] = None
+    position: Optional[Any] = None
 
 
 @dataclass(frozen=True)
@@ -86,6 +115,22 @@ class LinearAttentionSpec:
     decay: Tuple[float, ...]
     out_norm: Any = None
     output_gate: bool = True
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a decay per key channel and token: q = W_q x * head_dim^(-1/2), k = W_k x,
+    v = W_v x; alpha = sigmoid(W_a2 (W_a1 x) + b)^(1/tau) laid out heads x head_dim (``decay_rank`` the inner
+    size of the two-step projection); per head S_t = diag(alpha_t) S_(t-1) + k_t v_t^T (state
+    [head_dim, v_head_dim], float32, zero at the start), o_t = S_t^T q_t; each head's o through an RMS norm
+    over v_head_dim with one weight shared by the heads, times silu(W_g x), then the output projection."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    decay_rank: int
+    tau: float
+    norm_eps: float
 
 
 @dataclass(frozen=True)
@@ -107,9 +152,30 @@ class DenseMLPSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
-    """down(act(gate(x)) * up(x)) without bias."""
+    """down(act(gate(x)) * up(x)) without bias; ``activation`` "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi)
+    (z + 0.044715 z^3)))). ``names``: the tensors' names under the part's prefix (gate, up, down)."""
     hidden_size: int
     intermediate_size: int
+    activation: str = "silu"
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """Mixture of experts: ``num_experts`` gated feed-forwards (tensors ``e<i>.gate/up/down``, inner size
+    ``expert_ff``) of which a token uses ``top``. Router: s = sigmoid(W_router x) in float32; the choice goes by
+    s + ``correction`` (a tensor), among the experts of the ``keep_groups`` best of ``groups`` equal groups of
+    neighbours (group score: the sum of its two largest choice scores), the ``top`` largest; the weights are the
+    chosen s over their sum (+ 1e-20), times ``route_scale``. ``shared_ff``: a shared expert of that inner size
+    (``shared.gate/up/down``) runs for every token, times sigmoid(w_sg . x) (``shared.sg`` [1, hidden])."""
+    hidden_size: int
+    expert_ff: int
+    num_experts: int
+    top: int
+    groups: int = 1
+    keep_groups: int = 1
+    route_scale: float = 1.0
+    shared_ff: Optional[int] = None
     activation: str = "silu"
 
 
@@ -126,6 +192,21 @@ class LayerSpec:
     # checkpoint name of each sub-part under the prefix
     names: Tuple[Tuple[str, str], ...] = (("norm_in", "input_layernorm."), ("mixer", "self_attn."),
                                           ("norm_post", "post_attention_layernorm."), ("feed_forward", "mlp."))
+
+
+@dataclass(frozen=True)
+class PostNormLayerSpec:
+    """One block with the norm after the sum: x <- norm_mix(alpha * x + mixer(x)), then
+    x <- norm_ff(alpha * x + feed_forward(x)); the sublayers read x itself. Without a feed-forward the second
+    step, its norm and their names fall away."""
+    prefix: str
+    mixer: Any
+    norm_mix: Any
+    feed_forward: Any
+    norm_ff: Any
+    alpha: float = 1.0
+    names: Tuple[Tuple[str, str], ...] = (("mixer", "mix."), ("norm_mix", "norm1"), ("feed_forward", "mlp."),
+                                          ("norm_ff", "norm2"))
 
 
 @dataclass(frozen=True)

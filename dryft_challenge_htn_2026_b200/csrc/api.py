@@ -681,12 +681,13 @@ def kv_write(k, v, k_store, v_store, row_pos, row_seq, page_table, n_kv_heads, h
 
 
 def attention_masked(q, out, gate, out_scale, k_store, v_store, row_pos, row_seq, page_table, n_heads, n_kv_heads,
-                     head_dim, v_head_dim, window, chunk, scale, r1=None, r2=None, sink=None):
+                     head_dim, v_head_dim, window, chunk, scale, r1=None, r2=None, sink=None, softcap=None, keep_first=0):
     """Float32-arithmetic attention of every token row over its sequence's cached keys: causal, inside
     the row's chunk (``chunk`` positions, 0: none) and window (0: none); score = q.k * scale
     - r1_h * ln(1 + r2_h * distance) (with r1, r2 float32 [nh]); exp(sink_h) joins the denominator (with
-    sink); out = heads * sigmoid(gate) (with gate) * out_scale. q, gate and out may be rows of wider
-    matrices. Any phase; float32 or bfloat16 storage."""
+    sink); out = heads * sigmoid(gate) (with gate) * out_scale. ``softcap``: the score (before the bias)
+    becomes cap * tanh(score / cap). ``keep_first``: keys at positions below it stay in sight when the window
+    has moved on. q, gate and out may be rows of wider matrices. Any phase; float32 or bfloat16 storage."""
     _need_rows(q, "q"), _need_rows(out, "out", q.dtype), _need_rows(gate, "gate", q.dtype)
     _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", q.dtype), _need(v_store, "v_store", q.dtype)
@@ -702,7 +703,7 @@ def attention_masked(q, out, gate, out_scale, k_store, v_store, row_pos, row_seq
                                         c_float(out_scale), _p(k_store), _p(v_store), _p(row_pos), _p(row_seq),
                                         _p(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
                                         v_head_dim, int(window or 0), int(chunk or 0), c_float(scale), _p(r1), _p(r2),
-                                        _p(sink), _stream()), "attention_masked")
+                                        _p(sink), c_float(softcap or 0.0), int(keep_first or 0), _stream()), "attention_masked")
 
 
 MASKED_TILE_ROWS = 64            # queries a block of attention_masked_prefill_bf16 takes
@@ -931,15 +932,170 @@ def linear_attention_chunk_bf16(q, k, v, out, state, cu_q, seq_slot, decay, n_se
                                                    _stream()), "linear_attention_chunk_bf16", 2)
 
 
-def norm_gate(o, weight, eps, gate, out_scale, out):
+def norm_gate(o, weight, eps, gate, out_scale, out, group=None, gate_act="sigmoid"):
     """out = rmsnorm(o) * weight * sigmoid(gate) * out_scale, the norm over each whole row of o
-    (float32 [T, n]); gate and out in the storage type, possibly rows of wider matrices."""
+    (float32 [T, n]), or with ``group`` over each run of that many columns (one head) with a weight of
+    that size; ``gate_act`` "silu": gate * sigmoid(gate) instead. gate and out in the storage type,
+    possibly rows of wider matrices."""
     _need(o, "o", torch.float32, 2), _need(weight, "weight", torch.float32, 1)
     _need_rows(gate, "gate", out.dtype), _need_rows(out, "out")
     n = o.shape[1]
-    if weight.numel() != n or out.shape != o.shape or (gate is not None and gate.shape != o.shape):
+    group = n if group is None else int(group)
+    if group < 1 or n % group or weight.numel() != group or out.shape != o.shape or \
+            (gate is not None and gate.shape != o.shape) or gate_act not in ("sigmoid", "silu"):
         raise KernelError("norm_gate: shapes do not match")
     lib = _lib("linear_attention.cu")
     _check(lib, lib.dk_norm_gate(_dt(out), _p(o), _p(weight), c_float(eps), _p(gate),
                                  c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale), _p(out),
-                                 c_longlong(out.stride(0)), o.shape[0], n, _stream()), "norm_gate")
+                                 c_longlong(out.stride(0)), o.shape[0], n, group, int(gate_act == "silu"), _stream()),
+           "norm_gate")
+
+
+def gated_linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, z, z_bias, tau, q_scale, n_seq, n_heads,
+                                head_dim, v_head_dim):
+    """Gated linear attention token by token: S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_scale q_t) with the
+    decay of every key channel alpha_t = sigmoid(z_t + z_bias)^(1/tau) (z float32 [T, nh*hd], worked out in
+    float32 inside the kernel). Rows, state, padding and ``cu_q`` as in ``linear_attention_step``."""
+    _need_rows(q, "q"), _need_rows(k, "k", q.dtype), _need_rows(v, "v", q.dtype)
+    _need(out, "out", torch.float32, 2), _need(state, "state", torch.float32, 4)
+    _need(z, "z", torch.float32, 2), _need(z_bias, "z_bias", torch.float32, 1)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.shape[1] != n_heads * head_dim or \
+            v.shape[1] != n_heads * v_head_dim or tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or \
+            z.shape != (q.shape[0], n_heads * head_dim) or z_bias.numel() != n_heads * head_dim or \
+            head_dim > 256 or v_head_dim > 256 or not tau > 0:
+        raise KernelError("gated_linear_attention_step: shapes do not match (head sizes up to 256)")
+    lib = _lib("linear_attention.cu")
+    _check(lib, lib.dk_gated_linear_attention_step(_dt(q), _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(out), _p(state),
+                                                   _p(cu_q), _p(seq_pos0), _p(seq_slot), _p(z), _p(z_bias),
+                                                   c_float(1.0 / tau), c_float(q_scale), n_seq, n_heads, head_dim,
+                                                   v_head_dim, _stream()), "gated_linear_attention_step")
+
+
+# ------------------------------------------------------------------------ norm after the sum, casts
+def scale_add_rmsnorm(h, alpha, delta, norm_w, eps, a_out):
+    """h = rmsnorm(alpha * h + delta) * norm_w, written back to the float32 stream, and a_out = the same in
+    the storage type. ``delta`` a tensor or a ``Partial``."""
+    delta, parts, n_parts, stride = _parts(delta)
+    _need(h, "h", torch.float32, 2), _need(delta, "delta", a_out.dtype, 2), _need(norm_w, "norm_w", torch.float32, 1)
+    _need(a_out, "a_out", None, 2)
+    if a_out.shape != h.shape or norm_w.numel() != h.shape[1] or (delta is not None and delta.shape != h.shape):
+        raise KernelError("scale_add_rmsnorm: shapes do not match")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_scale_add_rmsnorm(_dt(a_out), _p(h), c_float(alpha), _p(delta), parts, n_parts, stride, _p(norm_w),
+                                         c_float(eps), h.shape[0], h.shape[1], _p(a_out), _stream()), "scale_add_rmsnorm")
+
+
+def cast_rows(h, a_out):
+    """a_out = h (float32) in a_out's type."""
+    _need(h, "h", torch.float32, 2), _need(a_out, "a_out", None, 2)
+    if a_out.shape != h.shape:
+        raise KernelError("cast_rows: shapes do not match")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_cast_rows(_dt(a_out), _p(h), _p(a_out), c_longlong(h.numel()), _stream()), "cast_rows")
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
+def act_mul(gu, out, act):
+    """out[r, c] = act(gu[r, c]) * gu[r, I + c] for gu [rows, 2I]; act ACT_SILU or ACT_GELU_TANH."""
+    _need(gu, "gu", None, 2), _need(out, "out", gu.dtype, 2)
+    if gu.shape != (out.shape[0], 2 * out.shape[1]):
+        raise KernelError("act_mul: shapes do not match")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_act_mul(_dt(gu), _p(gu), _p(out), c_longlong(gu.shape[0]), out.shape[1], int(act), _stream()), "act_mul")
+
+
+# ------------------------------------------- short convolution, head norm and rotation before a cache
+SHORT_CONV_MAX_TAPS = 9
+
+
+def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos, sin, rot_dims, row_pos, row_seq, seq_pos0,
+                   seq_slot, n_heads, n_kv_heads, head_dim, v_head_dim):
+    """Rows [q | k | v] of a fused projection -> ``out`` rows of the same layout: a causal convolution of
+    ``taps`` taps over time on every channel (``w_conv`` [channels, taps]; earlier rows of the same step, or
+    the sequence's ``state`` [slots, taps-1, channels] for positions before it), then per q and k head an RMS
+    norm with weights of the head's size, then the rotate-half rotation of the first ``rot_dims`` coordinates
+    by cos/sin [positions, rot_dims/2]. Each step optional (taps 1, weights None, rot_dims 0). The state is
+    only read: ``conv_state_update`` moves it on afterwards."""
+    _need_rows(proj, "proj"), _need_rows(out, "out", proj.dtype)
+    C = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
+    _need(state, "state", proj.dtype, 3), _need(w_conv, "w_conv", proj.dtype, 2)
+    _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
+    _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
+    for t, n in ((row_pos, "row_pos"), (row_seq, "row_seq"), (seq_pos0, "seq_pos0"), (seq_slot, "seq_slot")):
+        _need(t, n, torch.int32, 1)
+    if proj.shape[1] != C or out.shape != proj.shape or not 1 <= taps <= SHORT_CONV_MAX_TAPS or \
+            (taps > 1 and (state is None or w_conv is None or tuple(state.shape[1:]) != (taps - 1, C) or tuple(w_conv.shape) != (C, taps))) or \
+            rot_dims % 2 or rot_dims > head_dim or (rot_dims and (cos is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape)) or \
+            max(head_dim, v_head_dim) > 256 or (q_norm_w is not None and q_norm_w.numel() != head_dim) or \
+            (k_norm_w is not None and k_norm_w.numel() != head_dim):
+        raise KernelError("conv_norm_rope: shapes do not match")
+    lib = _lib("short_conv.cu")
+    _check(lib, lib.dk_conv_norm_rope(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(out), c_longlong(out.stride(0)),
+                                      _p(state), _p(w_conv), int(taps), _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos),
+                                      _p(sin), int(rot_dims), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot),
+                                      proj.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, _stream()), "conv_norm_rope")
+
+
+def conv_state_update(proj, state, taps, cu_q, seq_pos0, seq_slot, n_seq):
+    """state[slot] <- the last taps-1 rows of each sequence's projection as it stands after this step
+    (``cu_q`` None: row s is sequence s with one token; seq_pos0[s] < 0: padding)."""
+    _need_rows(proj, "proj"), _need(state, "state", proj.dtype, 3)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
+    if tuple(state.shape[1:]) != (taps - 1, proj.shape[1]) or not 2 <= taps <= SHORT_CONV_MAX_TAPS:
+        raise KernelError("conv_state_update: shapes do not match")
+    lib = _lib("short_conv.cu")
+    _check(lib, lib.dk_conv_state_update(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(state), int(taps), proj.shape[1],
+                                         _p(cu_q), _p(seq_pos0), _p(seq_slot), n_seq, _stream()), "conv_state_update")
+
+
+# ------------------------------------------------------------------------------ mixture of experts
+MOE_MAX_EXPERTS = 256
+
+
+def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, idx, wt, shared_gate):
+    """Router of a mixture of experts, float32 arithmetic: s = sigmoid(w_router x); the ``top`` experts with the
+    largest s + correction among the ``keep`` best of ``groups`` groups of neighbours (group score: its two
+    largest s + correction) -> ``idx`` int32 [T, top]; ``wt`` float32 [T, top] = their s over the sum, times
+    ``scale``; ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given."""
+    _need(x, "x", None, 2), _need(w_router, "w_router", torch.float32, 2), _need(correction, "correction", torch.float32, 1)
+    _need(w_shared_gate, "w_shared_gate", torch.float32, 1), _need(idx, "idx", torch.int32, 2), _need(wt, "wt", torch.float32, 2)
+    _need(shared_gate, "shared_gate", torch.float32, 1)
+    T, W = x.shape
+    E = w_router.shape[0]
+    if w_router.shape[1] != W or idx.shape != (T, top) or wt.shape != (T, top) or E > MOE_MAX_EXPERTS or E % groups or \
+            not 1 <= keep <= groups or not 1 <= top <= min(E, 32) or (correction is not None and correction.numel() != E) or \
+            (w_shared_gate is not None and (w_shared_gate.numel() != W or shared_gate is None or shared_gate.numel() != T)):
+        raise KernelError("moe_route: shapes do not match (up to 256 experts, up to 32 chosen)")
+    lib = _lib("moe.cu")
+    _check(lib, lib.dk_moe_route(_dt(x), _p(x), W, _p(w_router), _p(correction), _p(w_shared_gate), E, int(top), int(groups),
+                                 int(keep), c_float(scale), _p(idx), _p(wt), _p(shared_gate), T, _stream()), "moe_route")
+
+
+def moe_up_rows(x, w_gate_up, idx, mid, act=0):
+    """mid[t * top + j] = act(gate_e x_t) * (up_e x_t) for e = idx[t, j]; w_gate_up [E, 2 ff, W] with an expert's
+    gate rows before its up rows. A warp per output, float32 sums."""
+    _need(x, "x", None, 2), _need(w_gate_up, "w_gate_up", x.dtype, 3), _need(idx, "idx", torch.int32, 2), _need(mid, "mid", x.dtype, 2)
+    T, W = x.shape
+    top, ff = idx.shape[1], mid.shape[1]
+    if w_gate_up.shape[1:] != (2 * ff, W) or mid.shape[0] != T * top or idx.shape[0] != T:
+        raise KernelError("moe_up_rows: shapes do not match")
+    lib = _lib("moe.cu")
+    _check(lib, lib.dk_moe_up_rows(_dt(x), _p(x), W, _p(w_gate_up), _p(idx), _p(mid), ff, top, T, int(act), _stream()), "moe_up_rows")
+
+
+def moe_down_rows(mid, w_down, idx, wt, shared, shared_gate, out):
+    """out[t] = sum_j wt[t, j] * down_e mid[t * top + j] (e = idx[t, j]) + shared_gate[t] * shared[t]; w_down
+    [E, W, ff]; ``shared`` [T, W] and its gate optional."""
+    _need(mid, "mid", None, 2), _need(w_down, "w_down", mid.dtype, 3), _need(idx, "idx", torch.int32, 2)
+    _need(wt, "wt", torch.float32, 2), _need(shared, "shared", mid.dtype, 2), _need(shared_gate, "shared_gate", torch.float32, 1)
+    _need(out, "out", mid.dtype, 2)
+    T, top = idx.shape
+    W, ff = w_down.shape[1:]
+    if mid.shape != (T * top, ff) or out.shape != (T, W) or wt.shape != (T, top) or (shared is not None and shared.shape != (T, W)):
+        raise KernelError("moe_down_rows: shapes do not match")
+    lib = _lib("moe.cu")
+    _check(lib, lib.dk_moe_down_rows(_dt(mid), _p(mid), _p(w_down), _p(idx), _p(wt), _p(shared), _p(shared_gate), _p(out), W, ff,
+                                     top, T, _stream()), "moe_down_rows")

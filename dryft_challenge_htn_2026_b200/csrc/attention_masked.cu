@@ -4,6 +4,8 @@
 //     a sliding window,
 //   * a distance bias taken off the score: r1_h * ln(1 + r2_h * (i - j)),
 //   * a sink: exp(sink_h) joins the softmax's denominator and nothing else,
+//   * a cap on the score, cap * tanh(score / cap), before the masks,
+//   * first tokens that a window keeps: key j < keep_first stays in sight of every later query,
 //   * an output gate: the head's output times sigmoid of a gate row, and a constant factor.
 // One warp per (token, query head), every phase (whole prompts, continued portions, single tokens);
 // all arithmetic in float32 whatever the storage type. q, the gate and the output are rows of wider
@@ -36,7 +38,7 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
                                         const int* row_seq, const int* page_table, int pt_stride, int n_tok, int nh,
                                         int nkv, int hd, int hdv, int window, int chunk, float scale,
                                         const float* __restrict__ r1, const float* __restrict__ r2,
-                                        const float* __restrict__ sink) {
+                                        const float* __restrict__ sink, float softcap, int keep_first) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -63,7 +65,10 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
     float m = -INFINITY, l = 0.f;
     int lo = window > 0 ? max(0, pos - window + 1) : 0;
     if (chunk > 0) lo = max(lo, pos / chunk * chunk);
-    for (int j = lo; j <= pos; j++) {
+    // the kept first tokens that the window has left behind, then the window (or chunk) itself
+    const int kept = min(keep_first, lo);
+    for (int jj = lo - kept; jj <= pos; jj++) {
+        const int j = jj < lo ? jj - (lo - kept) : jj;
         const int page = pt[j / DK_PAGE];
         const T* kr = k_store + kv_offset(page, nkv, kvh, j % DK_PAGE, hd);
         const T* vr = v_store + kv_offset(page, nkv, kvh, j % DK_PAGE, hdv);
@@ -74,6 +79,7 @@ __global__ void attention_masked_kernel(const T* q, long long ldq, T* out, long 
             if (d < hd) dot += qv[i] * to_f(kr[d]);
         }
         float s = warp_sum(dot) * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         if (r1) s -= b1 * log1pf(b2 * (float)(pos - j));
         const float m_new = fmaxf(m, s);
         const float alpha = expf(m - m_new);  // m = -inf on the first key: alpha = 0
@@ -119,7 +125,8 @@ DK_EXPORT int dk_attention_masked(int dtype, const void* q, long long ldq, void*
                                   long long ldg, float out_scale, const void* k_store, const void* v_store,
                                   const int* row_pos, const int* row_seq, const int* page_table, int pt_stride,
                                   int n_tok, int nh, int nkv, int hd, int hdv, int window, int chunk, float scale,
-                                  const float* r1, const float* r2, const float* sink, cudaStream_t st) {
+                                  const float* r1, const float* r2, const float* sink, float softcap, int keep_first,
+                                  cudaStream_t st) {
     if (hd > 256 || hdv > 256 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)n_tok * nh;
     const unsigned blocks = (unsigned)((warps + 3) / 4);
@@ -127,8 +134,8 @@ DK_EXPORT int dk_attention_masked(int dtype, const void* q, long long ldq, void*
         return dk_launch(attention_masked_kernel<float>, dim3(blocks), dim3(128), 0, st, (const float*)q, ldq,
                          (float*)out, ldo, (const float*)gate, ldg, out_scale, (const float*)k_store,
                          (const float*)v_store, row_pos, row_seq, page_table, pt_stride, n_tok, nh, nkv, hd, hdv, window,
-                         chunk, scale, r1, r2, sink);
+                         chunk, scale, r1, r2, sink, softcap, keep_first);
     return dk_launch(attention_masked_kernel<bf16>, dim3(blocks), dim3(128), 0, st, (const bf16*)q, ldq, (bf16*)out, ldo,
                      (const bf16*)gate, ldg, out_scale, (const bf16*)k_store, (const bf16*)v_store, row_pos, row_seq,
-                     page_table, pt_stride, n_tok, nh, nkv, hd, hdv, window, chunk, scale, r1, r2, sink);
+                     page_table, pt_stride, n_tok, nh, nkv, hd, hdv, window, chunk, scale, r1, r2, sink, softcap, keep_first);
 }

@@ -30,7 +30,11 @@ __global__ void embed_rmsnorm_kernel(const int* tok, const T* __restrict__ embed
     }
     ss = block_sum(ss, red);
     const float rs = rsqrtf(ss / (float)H + eps);
-    if (w == nullptr) return;
+    if (w == nullptr) {   // no norm: a, when given, is the row itself in the storage type
+        if (a != nullptr)
+            for (int i = threadIdx.x; i < H; i += blockDim.x) a[row * H + i] = from_f<T>(hr[i]);
+        return;
+    }
     T* ar = a + row * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(hr[i] * rs * w[i]);
 }
@@ -679,4 +683,77 @@ DK_EXPORT int dk_xielu(int dtype, const void* z, void* out, long long n, float a
                          (bf16*)out, (size_t)(n / 8), ap, an);
     DISPATCH_T(dtype, return dk_launch(xielu_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const T*)z,
                                        (T*)out, (size_t)n, ap, an));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Norm after the sum: h[row] = rmsnorm(alpha * h[row] + delta[row]) * w, written back to the float32
+// stream, and a[row] = the same in the storage type (what the next sublayer reads). delta as a tensor
+// or as n_parts float32 partial sums. The sum, its mean square and the scaling are float32.
+template <typename T>
+__global__ void scale_add_rmsnorm_kernel(float* h, float alpha, const T* delta, const float* parts, int n_parts,
+                                         size_t part_stride, const float* __restrict__ w, float eps, int H, T* a) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row = blockIdx.x;
+    float* hr = h + row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float d = delta ? to_f(delta[row * H + i]) : 0.f;
+        for (int k = 0; k < n_parts; k++) d += parts[(size_t)k * part_stride + row * H + i];
+        const float v = fmaf(alpha, hr[i], d);
+        hr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = 1.f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = hr[i] * rs * w[i];
+        hr[i] = v;
+        a[row * H + i] = from_f<T>(v);
+    }
+}
+
+DK_EXPORT int dk_scale_add_rmsnorm(int dtype, float* h, float alpha, const void* delta, const float* parts, int n_parts,
+                                   long long part_stride, const float* w, float eps, int n_rows, int H, void* a,
+                                   cudaStream_t st) {
+    DISPATCH_T(dtype, return dk_launch(scale_add_rmsnorm_kernel<T>, dim3(n_rows), dim3(row_threads(H)), 0, st, h, alpha,
+                                       (const T*)delta, parts, n_parts, (size_t)part_stride, w, eps, H, (T*)a));
+}
+
+// a[row] = h[row] in the storage type (the stream as a sublayer's input, where no kernel before left it).
+template <typename T>
+__global__ void cast_rows_kernel(const float* h, T* a, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = from_f<T>(h[i]);
+}
+
+DK_EXPORT int dk_cast_rows(int dtype, const float* h, void* a, long long n, cudaStream_t st) {
+    DISPATCH_T(dtype, return dk_launch(cast_rows_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, h, (T*)a,
+                                       (size_t)n));
+}
+
+// out[r, c] = act(gu[r, c]) * gu[r, I + c] for rows [gate | up]; act 0: SiLU, 1: the tanh form of GELU,
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))). Arithmetic in float32.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <typename T>
+__global__ void act_mul_kernel(const T* gu, T* out, size_t n, int I, int act) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    size_t r = idx / I, c = idx % I;
+    const float g = to_f(gu[r * 2 * I + c]);
+    const float u = to_f(gu[r * 2 * I + I + c]);
+    out[idx] = from_f<T>((act == 1 ? gelu_tanh_f(g) : g / (1.f + expf(-g))) * u);
+}
+
+DK_EXPORT int dk_act_mul(int dtype, const void* gu, void* out, long long n_rows, int I, int act, cudaStream_t st) {
+    size_t n = (size_t)n_rows * I;
+    DISPATCH_T(dtype, return dk_launch(act_mul_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
+                                       (const T*)gu, (T*)out, n, I, act));
 }

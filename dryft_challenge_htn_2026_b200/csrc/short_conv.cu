@@ -1,0 +1,147 @@
+// What stands between an attention mixer's fused projection and its cache, for mixers that ask for it:
+//   * a short causal convolution over time on every channel of q, k and v,
+//       y_t[c] = sum_j w[c][j] * u_(t - taps + 1 + j)[c],   zeros before the sequence's start,
+//     whose memory, the last taps - 1 projected rows of each sequence, is a per-sequence state
+//     [slots, taps - 1, channels] (zero when a slot is taken, so that the zeros come by themselves);
+//   * an RMS norm over each query and key head with a weight of the head's size,
+//   * a rotate-half rotation of the first rot_dims coordinates of each query and key head (coordinate i
+//     with i + rot_dims / 2) by angles from a table [positions, rot_dims / 2]; the rest pass.
+// Each option may be left out (taps = 1, no norm weights, rot_dims = 0). The result is a dense row
+// [q heads | k heads | v heads] in the storage type; sums, norms and the rotation are float32.
+// A second kernel moves the state on once the first has read it.
+#include "common.cuh"
+
+#define SC_THREADS 128
+#define SC_MAX_TAPS 9
+
+// One block per (token row, head of q, k or v). Rows with position < 0 are padding.
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const T* state, const T* __restrict__ wconv,
+                      int taps, const float* __restrict__ qn, const float* __restrict__ kn, float eps,
+                      const float* __restrict__ cosv, const float* __restrict__ sinv, int rot_dims, const int* row_pos,
+                      const int* row_seq, const int* seq_pos0, const int* seq_slot, int nh, int nkv, int hd, int hdv) {
+    __shared__ float red[33];
+    __shared__ float ys[256];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x, head = blockIdx.y;
+    const int pos = row_pos[t];
+    if (pos < 0) return;
+    const int s = row_seq[t];
+    const int p0 = seq_pos0[s];
+    const int C = nh * hd + nkv * hd + nkv * hdv;
+    int c0, size;
+    const float* wn = nullptr;
+    if (head < nh) { c0 = head * hd; size = hd; wn = qn; }
+    else if (head < nh + nkv) { c0 = nh * hd + (head - nh) * hd; size = hd; wn = kn; }
+    else { c0 = (nh + nkv) * hd + (head - nh - nkv) * hdv; size = hdv; }
+    const bool rotates = head < nh + nkv && rot_dims > 0;
+    const T* st = taps > 1 ? state + (size_t)seq_slot[s] * (taps - 1) * C : nullptr;
+    float y[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int d = threadIdx.x + r * SC_THREADS;
+        y[r] = 0.f;
+        if (d < size) {
+            const int c = c0 + d;
+            float acc = 0.f;
+            for (int j = 0; j < taps; j++) {
+                const int back = taps - 1 - j;                 // u at position pos - back
+                const int pp = pos - back;
+                const float u = pp >= p0 ? to_f(proj[(size_t)(t - back) * ld + c])
+                                         : to_f(st[(size_t)(taps - 1 - (p0 - pp)) * C + c]);
+                const float w = taps > 1 ? to_f(wconv[(size_t)c * taps + j]) : 1.f;
+                acc = fmaf(w, u, acc);
+            }
+            y[r] = acc;
+            ss += acc * acc;
+        }
+    }
+    if (wn != nullptr) {
+        ss = block_sum(ss, red);
+        const float rs = 1.f / sqrtf(ss / (float)size + eps);
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int d = threadIdx.x + r * SC_THREADS;
+            if (d < size) y[r] *= rs * wn[d];
+        }
+    }
+    if (rotates) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int d = threadIdx.x + r * SC_THREADS;
+            if (d < size) ys[d] = y[r];
+        }
+        __syncthreads();
+        const int half = rot_dims / 2;
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int d = threadIdx.x + r * SC_THREADS;
+            if (d < rot_dims) {
+                const int i = d < half ? d : d - half;
+                const float c = cosv[(size_t)pos * half + i], sn = sinv[(size_t)pos * half + i];
+                y[r] = d < half ? ys[d] * c - ys[d + half] * sn : ys[d] * c + ys[d - half] * sn;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int d = threadIdx.x + r * SC_THREADS;
+        if (d < size) out[(size_t)t * ldo + c0 + d] = from_f<T>(y[r]);
+    }
+}
+
+// state[slot] <- the last taps - 1 projected rows of the sequence as it stands after this step: rows of
+// this step where it brought enough, the newest of the old state before them where it did not.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* proj, long long ld, T* state, int taps, int C, const int* cu_q,
+                                         const int* seq_pos0, const int* seq_slot) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C || seq_pos0[s] < 0) return;
+    const int r0 = cu_q ? cu_q[s] : s, len = cu_q ? cu_q[s + 1] - r0 : 1;   // no cu_q: row s is sequence s, one token
+    T* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
+    T old[SC_MAX_TAPS - 1];
+#pragma unroll
+    for (int i = 0; i < SC_MAX_TAPS - 1; i++)
+        if (i < taps - 1) old[i] = st[(size_t)i * C + c];
+#pragma unroll
+    for (int i = 0; i < SC_MAX_TAPS - 1; i++) {
+        if (i < taps - 1) {
+            const int r = len - (taps - 1) + i;              // row of this step that lands in place i
+            st[(size_t)i * C + c] = r >= 0 ? proj[(size_t)(r0 + r) * ld + c] : old[i + len];
+        }
+    }
+}
+
+DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void* out, long long ldo, const void* state,
+                                const void* wconv, int taps, const float* qn, const float* kn, float eps,
+                                const float* cosv, const float* sinv, int rot_dims, const int* row_pos,
+                                const int* row_seq, const int* seq_pos0, const int* seq_slot, int n_tok, int nh, int nkv,
+                                int hd, int hdv, cudaStream_t st) {
+    if (hd > 256 || hdv > 256 || taps < 1 || taps > SC_MAX_TAPS || rot_dims > hd || rot_dims % 2)
+        return (int)cudaErrorInvalidValue;
+    const dim3 grid(n_tok, nh + 2 * nkv), block(SC_THREADS);
+    if (dtype == 0)
+        return dk_launch(conv_norm_rope_kernel<float>, grid, block, 0, st, (const float*)proj, ld, (float*)out, ldo,
+                         (const float*)state, (const float*)wconv, taps, qn, kn, eps, cosv, sinv, rot_dims, row_pos,
+                         row_seq, seq_pos0, seq_slot, nh, nkv, hd, hdv);
+    return dk_launch(conv_norm_rope_kernel<bf16>, grid, block, 0, st, (const bf16*)proj, ld, (bf16*)out, ldo,
+                     (const bf16*)state, (const bf16*)wconv, taps, qn, kn, eps, cosv, sinv, rot_dims, row_pos, row_seq,
+                     seq_pos0, seq_slot, nh, nkv, hd, hdv);
+}
+
+DK_EXPORT int dk_conv_state_update(int dtype, const void* proj, long long ld, void* state, int taps, int C,
+                                   const int* cu_q, const int* seq_pos0, const int* seq_slot, int n_seq, cudaStream_t st) {
+    if (taps < 2 || taps > SC_MAX_TAPS) return (int)cudaErrorInvalidValue;
+    const dim3 grid(n_seq, (C + 127) / 128), block(128);
+    if (dtype == 0)
+        return dk_launch(conv_state_update_kernel<float>, grid, block, 0, st, (const float*)proj, ld, (float*)state,
+                         taps, C, cu_q, seq_pos0, seq_slot);
+    return dk_launch(conv_state_update_kernel<bf16>, grid, block, 0, st, (const bf16*)proj, ld, (bf16*)state, taps, C,
+                     cu_q, seq_pos0, seq_slot);
+}

@@ -10,6 +10,7 @@ from ..csrc.api import PAGE
 from ..registry import config_from_folder
 from ..sampling import SamplingParams, request_seed
 from ..weights import bind_random, load_weights
+from ..weights.loader import list_tensors
 from .generate import GpuBackend, plan_batches, run_batch
 from .model import CausalLM
 from .runner import Runner
@@ -27,6 +28,8 @@ def _dtype(dtype):
 def load_model(model_path, dtype=torch.bfloat16, device="cuda"):
     """The model class is chosen by config.json's ``architectures``; weights by tensor name."""
     config = config_from_folder(model_path)
+    if hasattr(config, "with_shapes"):      # sizes that only the tensors' shapes give
+        config = config.with_shapes({name: shape for name, (_, shape) in list_tensors(model_path).items()})
     model = CausalLM(config.to_spec(), _dtype(dtype), device)
     load_weights(model, model_path)
     return model

@@ -110,10 +110,14 @@ class CausalLM:
         a = torch.empty((ctx.n_tok, s.hidden_size), dtype=rt.dtype, device=rt.device)
         first = self.blocks[s.schedule[0].layer]
         # the embedding kernel computes RMSNorm and nothing else, and only of the embedding as it leaves the kernel
-        fused = isinstance(first.norm_in, RMSNorm) and not (s.schedule[0].add_embedding or s.schedule[0].add_row)
+        fused = isinstance(getattr(first, "norm_in", None), RMSNorm) and not (s.schedule[0].add_embedding or s.schedule[0].add_row)
         norm_w, eps = (first.norm_in.weight, first.norm_in.spec.eps) if fused else (None, 0.0)
+        ctx.stream_copy = None   # the stream in the storage type, where a kernel has left it (blocks with the norm after the sum)
+        plain = getattr(first, "reads_stream", False) and not (s.schedule[0].add_embedding or s.schedule[0].add_row)
         if self.position is None and s.embed_scale == 1.0:
-            api.embed_rmsnorm(ctx.tok, self.embed, norm_w, eps, h, a)
+            api.embed_rmsnorm(ctx.tok, self.embed, norm_w, eps, h, a if (fused or plain) else None)
+            if plain:
+                ctx.stream_copy = a
         else:
             api.embed_position_rmsnorm(ctx.tok, self.embed, s.embed_scale, ctx.row_pos,
                                        self.position.inv_freq if self.position is not None else None, norm_w, eps, h, a)
@@ -123,10 +127,12 @@ class CausalLM:
             if e.add_embedding or e.add_row is not None:
                 api.stream_add(h, e0 if e.add_embedding else None,
                                self.tables[e.add_row[0]][e.add_row[1]] if e.add_row is not None else None)
+                ctx.stream_copy = None
             pending = self.blocks[e.layer].forward(ctx, h, pending, cache.views(e.cache), e.writes,
                                                    a if (i == 0 and fused) else None)
             if tap is not None:
-                tap(i, h + (pending.ws.sum(0) if isinstance(pending, api.Partial) else pending.to(torch.float32)))
+                tap(i, h.clone() if pending is None else
+                    h + (pending.ws.sum(0) if isinstance(pending, api.Partial) else pending.to(torch.float32)))
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
         an = add_norm(self.final_norm, h, pending, rt.dtype, rows=ctx.want_rows)

@@ -2,8 +2,11 @@
 window, a logarithmic distance bias, a sink in the softmax's denominator and an output gate, each
 switched on by its specification; key and value heads may differ in size.
 
-forward = one fused projection [q; k; v; gate] -> k and v into the cache -> attention over the cache
-with the gate in its epilogue -> output projection. Kernels: bfloat16 prompts with equal head sizes of 64
+forward = one fused projection [q; k; v; gate] -> (where the specification asks: a short causal convolution
+over time on q, k and v with a per-sequence state, a norm per q and k head, a rotation of the heads' first
+coordinates; one kernel) -> k and v into the cache -> attention over the cache with the gate in its epilogue
+-> output projection. Further options of the scores: a cap, first tokens that the window keeps, a sink fixed
+at zero. Kernels: bfloat16 prompts with equal head sizes of 64
 or 128 on tcgen05 tensor cores, other head sizes in steps of 16 on mma.sync, single tokens by a kernel of
 their own, and float32 (or any other size) on the float32-arithmetic kernel that serves every phase. The part also runs as a branch of a
 ``ParallelMixer``, which does the projections of all its branches in one product each: ``mix`` takes
@@ -11,11 +14,11 @@ the projected rows and leaves scale * (gated heads) where the caller wants them.
 """
 import torch
 
-from ..cache.requests import KVRequest
+from ..cache.requests import KVRequest, StateRequest
 from ..config.specs import MaskedAttentionSpec
 from ..csrc import api
 from .attention import QueryTiles
-from .base import ParamDecl, Part, register_part
+from .base import ParamDecl, Part, build_part, register_part
 from .linear import linear
 
 
@@ -33,9 +36,28 @@ class MaskedAttention(Part):
         self.n_v, self.n_mid = s.num_kv_heads * s.v_head_dim, s.num_heads * s.v_head_dim
         self.n_in = self.n_q + self.n_k + self.n_v + (self.n_mid if s.output_gate else 0)
         self.r1 = self.r2 = self.sink = None
+        if s.unit_sink:
+            if s.sink:
+                raise ValueError("a learned sink and a sink fixed at zero exclude each other")
+            self.sink = torch.zeros(s.num_heads, dtype=torch.float32, device=rt.device)   # exp(0) = 1 in the denominator
+        if s.keep_first < 0 or (s.softcap is not None and not s.softcap > 0):
+            raise ValueError(f"keep_first {s.keep_first} / softcap {s.softcap}")
+        # what stands between the projection and the cache
+        self.taps = int(s.conv_taps or 1)
+        if not 1 <= self.taps <= api.SHORT_CONV_MAX_TAPS:
+            raise ValueError(f"a convolution of {s.conv_taps} taps (1 to {api.SHORT_CONV_MAX_TAPS})")
+        self.qk_norm = s.qk_norm
+        self.position = build_part(s.position, rt) if s.position is not None else None
+        if self.position is not None and self.position.spec.dim > s.head_dim:
+            raise ValueError(f"a rotation over {self.position.spec.dim} coordinates of heads of {s.head_dim}")
+        self.prepares = self.taps > 1 or self.qk_norm is not None or self.position is not None
+        self.n_qkv = self.n_q + self.n_k + self.n_v
+        self.q_norm_w = self.k_norm_w = self.w_conv = None
+        self.max_positions = 0
         # the tensor-core kernels take bfloat16 with head sizes in steps of 16; everything else (float32, odd
         # head sizes) runs on the float32-arithmetic kernel, which serves every phase
-        self.tensor_core = rt.dtype == torch.bfloat16 and api.masked_bf16_takes(s.head_dim, s.v_head_dim)
+        self.tensor_core = rt.dtype == torch.bfloat16 and api.masked_bf16_takes(s.head_dim, s.v_head_dim) \
+            and s.softcap is None and not s.keep_first
         self.tiles = QueryTiles(api.MASKED_TILE_ROWS) if self.tensor_core else None
         # equal head sizes of 64 or 128: prompts run on the tcgen05 kernel (its masked build), in tiles of 128 queries
         self.tc_tiles = QueryTiles(api.TC_TILE_ROWS) if self.tensor_core and s.head_dim == s.v_head_dim \
@@ -55,6 +77,12 @@ class MaskedAttention(Part):
                   ParamDecl("r2", (s.num_heads,), init="positive", keep_float32=True)]
         if s.sink:
             d.append(ParamDecl("sink", (s.num_heads,), init="unit", keep_float32=True))
+        if self.taps > 1:
+            d += [ParamDecl("q.conv", (self.n_q, self.taps), init="taps"), ParamDecl("k.conv", (self.n_k, self.taps), init="taps"),
+                  ParamDecl("v.conv", (self.n_v, self.taps), init="taps")]
+        if self.qk_norm is not None:
+            d += [ParamDecl("q.norm", (s.head_dim,), init="norm", keep_float32=True),
+                  ParamDecl("k.norm", (s.head_dim,), init="norm", keep_float32=True)]
         return d
 
     def bind(self, tensors):
@@ -68,23 +96,60 @@ class MaskedAttention(Part):
             self.r2 = tensors.pop("r2").to(torch.float32).contiguous()
         if self.spec.sink:
             self.sink = tensors.pop("sink").to(torch.float32).contiguous()
+        if self.taps > 1:
+            self.w_conv = torch.cat([tensors.pop("q.conv"), tensors.pop("k.conv"), tensors.pop("v.conv")], 0).contiguous()
+        if self.qk_norm is not None:
+            self.q_norm_w = tensors.pop("q.norm").to(torch.float32).contiguous()
+            self.k_norm_w = tensors.pop("k.norm").to(torch.float32).contiguous()
 
     def step_weights(self):
         return [self.w_in, self.w_o]
 
     def cache_requests(self):
         s = self.spec
-        return [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype, s.v_head_dim, s.chunk)]
+        r = [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype, s.v_head_dim, s.chunk, s.keep_first)]
+        if self.taps > 1:     # the convolution's memory: the last taps - 1 projected rows [q | k | v] of a sequence
+            r.append(StateRequest((self.taps - 1, self.n_qkv), self.rt.dtype))
+        return r
+
+    def prepare(self, max_positions):
+        self.max_positions = max_positions
+        if self.position is not None:
+            self.position.tables(max_positions)
+
+    def prepared_rows(self, ctx, views, proj, writes=True):
+        """[q | k | v] of the projection rows after the convolution, the head norm and the rotation, as a dense
+        matrix; the convolution's state moves on behind it."""
+        s = self.spec
+        if not writes and self.taps > 1:
+            raise ValueError("a layer with a short convolution cannot run on another layer's cache entry")
+        out = torch.empty((ctx.n_tok, self.n_qkv), dtype=self.rt.dtype, device=self.rt.device)
+        state = views[1].state if self.taps > 1 else None
+        cos = sin = None
+        rot = 0
+        if self.position is not None:
+            rot = self.position.spec.dim
+            cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1))
+        pos0 = ctx.row_pos if ctx.is_decode else ctx.seq_pos0     # one token a row: its position is what came before
+        qkv = proj[:, :self.n_qkv]
+        api.conv_norm_rope(qkv, out, state, self.w_conv, self.taps, self.q_norm_w, self.k_norm_w,
+                           self.qk_norm.eps if self.qk_norm is not None else 0.0, cos, sin, rot, ctx.row_pos, ctx.row_seq,
+                           pos0, ctx.seq_slot, s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim)
+        if self.taps > 1:
+            api.conv_state_update(qkv, state, self.taps, None if ctx.is_decode else ctx.cu_q, pos0, ctx.seq_slot, ctx.n_seq)
+        return out
 
     def mix(self, ctx, views, proj, mid, scale, writes=True):
         """``proj`` [tokens, n_in]: this part's rows of a projection (possibly columns of a wider matrix);
         ``mid`` [tokens, n_mid]: where scale * (gated heads) go."""
         s, kv = self.spec, views[0]
         table = ctx.tables[kv.group]
+        gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
+        if self.prepares:
+            proj = self.prepared_rows(ctx, views, proj, writes)
         q = proj[:, :self.n_q]
         k = proj[:, self.n_q:self.n_q + self.n_k]
         v = proj[:, self.n_q + self.n_k:self.n_q + self.n_k + self.n_v]
-        gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
         sizes = (s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.window, s.chunk, s.scale)
         if self.tensor_core and ctx.is_decode and api.masked_decode_streams(q, mid, gate, s.head_dim, s.v_head_dim):
             # single tokens, keys and values of one size: the library's split decode kernel in its masked build
@@ -117,7 +182,7 @@ class MaskedAttention(Part):
             return api.attention_masked_prefill_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tiles.key], ctx.cu_q,
                                                      ctx.seq_pos0, table, *sizes, self.r1, self.r2, self.sink)
         api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, *sizes, self.r1, self.r2,
-                             self.sink)
+                             self.sink, s.softcap, s.keep_first)
 
     def forward(self, ctx, views, a, writes=True):
         proj = linear(a, self.w_in)

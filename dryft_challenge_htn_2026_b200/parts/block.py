@@ -8,7 +8,7 @@ norm that says ``takes_partial`` adds them up while it reads, for any other they
 """
 import torch
 
-from ..config.specs import LayerSpec
+from ..config.specs import LayerSpec, PostNormLayerSpec
 from ..csrc import api
 from .base import ParamDecl, Part, build_part, register_part
 
@@ -69,3 +69,52 @@ def add_norm(norm, h, delta, dtype, rows=None):
 
 
 register_part(LayerSpec, PreNormBlock)
+
+
+class PostNormBlock(Part):
+    """Norm after the sum: x <- norm_mix(alpha * x + mixer(x)), then x <- norm_ff(alpha * x + feed_forward(x)).
+    The residual stream stays float32; each norm kernel writes the stream back and leaves its copy in the
+    storage type, which is what the next sublayer (of this block or the next) reads: it travels as
+    ``ctx.stream_copy``. Nothing is left pending for the block after it."""
+    reads_stream = True      # the block's first sublayer reads the stream itself, not a norm of it
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.mixer = build_part(spec.mixer, rt)
+        self.norm_mix = build_part(spec.norm_mix, rt)
+        self.feed_forward = build_part(spec.feed_forward, rt) if spec.feed_forward is not None else None
+        self.norm_ff = build_part(spec.norm_ff, rt) if spec.feed_forward is not None else None
+        for n in (self.norm_mix, self.norm_ff):
+            if n is not None and not hasattr(n, "scale_add_forward"):
+                raise TypeError(f"{type(n).__name__} cannot stand after a sum: it has no scale_add_forward()")
+
+    _subparts = PreNormBlock._subparts
+    param_decls = PreNormBlock.param_decls
+    bind = PreNormBlock.bind
+    step_weights = PreNormBlock.step_weights
+    step_plans = PreNormBlock.step_plans
+    cache_requests = PreNormBlock.cache_requests
+    prepare = PreNormBlock.prepare
+
+    def forward(self, ctx, h, pending, views, writes=True, a=None):
+        dtype = self.rt.dtype
+        if pending is not None:          # a block before this one left its output to be added
+            if isinstance(pending, api.Partial):
+                pending = pending.sum(dtype)
+            api.stream_add(h, pending.to(torch.float32))
+            ctx.stream_copy = None
+        if a is None:
+            a = getattr(ctx, "stream_copy", None)
+        if a is None:
+            a = torch.empty(h.shape, dtype=dtype, device=h.device)
+            api.cast_rows(h, a)
+        d = self.mixer.forward(ctx, views, a, writes)
+        a = self.norm_mix.scale_add_forward(h, self.spec.alpha, d, torch.empty(h.shape, dtype=dtype, device=h.device))
+        if self.feed_forward is not None:
+            d = self.feed_forward.forward(ctx, a)
+            a = self.norm_ff.scale_add_forward(h, self.spec.alpha, d, torch.empty(h.shape, dtype=dtype, device=h.device))
+        ctx.stream_copy = a
+        return None
+
+
+register_part(PostNormLayerSpec, PostNormBlock)

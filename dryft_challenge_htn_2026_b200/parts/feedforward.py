@@ -12,28 +12,34 @@ from .linear import SILU, XIELU, linear
 class GatedMLP(Part):
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not implemented (silu only)")
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"activation {spec.activation!r} is not implemented (silu, gelu_tanh)")
         if rt.dtype == torch.bfloat16 and (spec.hidden_size % 8 or spec.intermediate_size % 8):
             raise ValueError("bfloat16 products need hidden and intermediate sizes that are multiples of 8, "
                              f"not {spec.hidden_size} / {spec.intermediate_size}")
 
     def param_decls(self):
         s = self.spec
-        return [ParamDecl("gate_proj.weight", (s.intermediate_size, s.hidden_size)),
-                ParamDecl("up_proj.weight", (s.intermediate_size, s.hidden_size)),
-                ParamDecl("down_proj.weight", (s.hidden_size, s.intermediate_size))]
+        g, u, d = s.names
+        return [ParamDecl(g, (s.intermediate_size, s.hidden_size)), ParamDecl(u, (s.intermediate_size, s.hidden_size)),
+                ParamDecl(d, (s.hidden_size, s.intermediate_size))]
 
     def bind(self, tensors):
         # gate rows then up rows, as the reference fuses them (engine/engine.py:304-306)
-        self.w_gate_up = torch.cat([tensors.pop("gate_proj.weight"), tensors.pop("up_proj.weight")], 0).contiguous()
-        self.w_down = tensors.pop("down_proj.weight").contiguous()
+        g, u, d = self.spec.names
+        self.w_gate_up = torch.cat([tensors.pop(g), tensors.pop(u)], 0).contiguous()
+        self.w_down = tensors.pop(d).contiguous()
 
     def step_weights(self):
         return [self.w_gate_up, self.w_down]
 
     def forward(self, ctx, a):
-        return linear(linear(a, self.w_gate_up, SILU), self.w_down, allow_partial=True)
+        if self.spec.activation == "silu":
+            return linear(linear(a, self.w_gate_up, SILU), self.w_down, allow_partial=True)
+        gu = linear(a, self.w_gate_up)
+        mid = torch.empty((gu.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
+        api.act_mul(gu, mid, api.ACT_GELU_TANH)
+        return linear(mid, self.w_down, allow_partial=True)
 
 
 register_part(GatedMLPSpec, GatedMLP)

@@ -1,7 +1,7 @@
 """RMSNorm (reference: engine/engine.py:107-110, engine/fused.py:152-172)."""
 import torch
 
-from ..config.specs import RMSNormSpec, ScalarRMSNormSpec
+from ..config.specs import OnePlusRMSNormSpec, RMSNormSpec, ScalarRMSNormSpec
 from ..csrc import api
 from .base import ParamDecl, Part, register_part
 
@@ -20,6 +20,12 @@ class RMSNorm(Part):
         """h (float32 residual stream) += delta (a tensor, a ``csrc.api.Partial`` or None);
         out = norm(h). ``rows``: only these rows, into out[0..len(rows)), leaving h as it is."""
         api.add_rmsnorm(h, delta, self.weight, self.spec.eps, out, rows)
+        return out
+
+    def scale_add_forward(self, h, alpha, delta, out):
+        """The norm after the sum: h = norm(alpha * h + delta), written back to the float32 stream; out = the
+        same in the storage type. ``delta`` a tensor or a ``csrc.api.Partial``."""
+        api.scale_add_rmsnorm(h, alpha, delta, self.weight, self.spec.eps, out)
         return out
 
 
@@ -41,3 +47,18 @@ class ScalarRMSNorm(RMSNorm):
 
 
 register_part(ScalarRMSNormSpec, ScalarRMSNorm)
+
+
+class OnePlusRMSNorm(RMSNorm):
+    """RMS norm whose stored weight sits around zero: y = (1 + w) * x * rsqrt(mean(x^2) + eps). One is added in
+    float32 when the tensor is bound, so the norm runs on the kernels of ``RMSNorm``. Like the scalar norm its
+    tensor is named by the part's prefix itself."""
+
+    def param_decls(self):
+        return [ParamDecl("", (self.spec.dim,), init="around_zero", keep_float32=True)]
+
+    def bind(self, tensors):
+        self.weight = (1.0 + tensors[""].to(torch.float32)).contiguous()
+
+
+register_part(OnePlusRMSNormSpec, OnePlusRMSNorm)

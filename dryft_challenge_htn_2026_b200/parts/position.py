@@ -10,7 +10,7 @@ cache write and cannot be combined with a per-head q/k norm (which would have to
 attention part refuses that pair."""
 import torch
 
-from ..config.specs import RotaryHalfSpec, SinusoidSpec
+from ..config.specs import RotaryHalfSpec, RotaryPartSpec, SinusoidSpec
 from .base import Part, register_part
 
 
@@ -49,3 +49,34 @@ class Sinusoid(Part):
 
 
 register_part(SinusoidSpec, Sinusoid)
+
+
+class RotaryPart(Part):
+    """Angle tables of a rotation over the first ``dim`` coordinates of a head: frequencies base^(-2i/dim) made
+    in float64 and rounded to float32 once, angle = float32(position) * frequency in float32, its cosine and
+    sine taken in float64 and rounded. The mixer that owns the part hands the tables and ``dim`` to the kernel
+    that rotates (``csrc.api.conv_norm_rope``)."""
+    fused_tables = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if spec.dim % 2 or spec.dim < 0:
+            raise ValueError(f"a rotation over {spec.dim} coordinates: the number must be even")
+        self._n = 0
+        self._cos = self._sin = None
+
+    def tables(self, n):
+        """cos, sin [>= n, dim/2] float32."""
+        if n > self._n:
+            n = max(n, 2 * self._n, 256)
+            dim = self.spec.dim
+            i = torch.arange(dim // 2, dtype=torch.float64)
+            freq = (float(self.spec.base) ** (-2.0 * i / dim)).to(torch.float32)
+            ang = (torch.arange(n, dtype=torch.float32)[:, None] * freq[None, :]).to(torch.float64)
+            self._cos = ang.cos().to(torch.float32).to(self.rt.device).contiguous()
+            self._sin = ang.sin().to(torch.float32).to(self.rt.device).contiguous()
+            self._n = n
+        return self._cos, self._sin
+
+
+register_part(RotaryPartSpec, RotaryPart)

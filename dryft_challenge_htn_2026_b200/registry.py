@@ -5,6 +5,7 @@ Adding an architecture: write a ``ModelConfig`` subclass with ``architecture``, 
 ``to_dict`` and ``to_spec``, then ``register_architecture(YourConfig)``."""
 from .config.base import ConfigError, read_config_json
 from .config.nilivik import NilivikConfig
+from .config.pibulix import PibulixConfig
 from .config.qwen3 import Qwen3Config
 
 _ARCHITECTURES = {}
@@ -43,3 +44,4 @@ def config_from_folder(folder):
 
 register_architecture(Qwen3Config)
 register_architecture(NilivikConfig)
+register_architecture(PibulixConfig)

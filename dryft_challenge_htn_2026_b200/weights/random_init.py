@@ -20,6 +20,12 @@ def _shape_draw(x, init, matrix_std, norm_std):
         return x
     if init == "positive":
         return 0.05 + 0.3 * x.abs()
+    if init == "around_zero":       # weights stored around zero (a norm that adds one; a router's correction)
+        return norm_std * x
+    if init == "taps":              # a short convolution's taps: of the order of one
+        return 0.5 * x
+    if init == "wide":              # matrices whose outputs should spread (routers, the second step of a decay)
+        return 10.0 * matrix_std * x
     return matrix_std * x
 
 
