@@ -12,14 +12,14 @@ blocks (``parts``), the paged cache (``cache``), the step function, generation l
 point (``engine``), sampling (``sampling``) and the CUDA kernels (``csrc``).
 """
 from .cache import Cache, CacheFull, KVRequest, StateRequest
-from .config import ConfigError, ModelConfig, ModelSpec, NilivikConfig, Qwen3Config
+from .config import ConfigError, ModelConfig, ModelSpec, NilivikConfig, PibulixConfig, Qwen3Config
 from .engine import CausalLM, Engine, Runner, load_model, random_model
 from .parts import Part, register_part
 from .registry import architectures, config_from_dict, config_from_folder, register_architecture
 from .sampling import SamplingParams
 from .weights import WeightError, load_weights, write_random_model
 
-__all__ = ["Cache", "CacheFull", "KVRequest", "StateRequest", "ConfigError", "ModelConfig", "ModelSpec", "NilivikConfig",
+__all__ = ["Cache", "CacheFull", "KVRequest", "StateRequest", "ConfigError", "ModelConfig", "ModelSpec", "NilivikConfig", "PibulixConfig",
            "Qwen3Config",
            "CausalLM", "Engine", "Runner", "load_model", "random_model", "Part", "register_part", "architectures",
            "config_from_dict", "config_from_folder", "register_architecture", "SamplingParams", "WeightError",

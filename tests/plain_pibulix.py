@@ -54,27 +54,39 @@ def visible(i, j, size, keep_first):
     return j <= i and (i - j < size or j < keep_first)
 
 
+def attention_core(q, k, v, scale, size, keep_first, softcap, pos0=0):
+    """q [T, H, D], k [T, G, D], v [T, G, V] at positions pos0.. -> [T, H, V]: capped scores, the window with its
+    kept first tokens, and a softmax whose denominator has one added."""
+    T, H, _ = q.shape
+    G, V = k.shape[1], v.shape[2]
+    out = torch.zeros(T, H, V, dtype=F)
+    see = torch.tensor([[visible(pos0 + i, pos0 + j, size if size else 1 << 60, keep_first) for j in range(T)] for i in range(T)])
+    for hd in range(H):
+        g = hd // (H // G)
+        s = (q[:, hd] @ k[:, g].T) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        e = torch.where(see, torch.exp(s), torch.zeros_like(s))
+        out[:, hd] = (e / (1.0 + e.sum(-1, keepdim=True))) @ v[:, g]
+    return out
+
+
 def attention_mixer(h, p, m, eps, pos0=0):
     """h [T, W]; p: tensors q, k, v, o, q.norm, k.norm, q.conv, k.conv, v.conv; m: the mixer's config."""
     T = h.shape[0]
     H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q, k, v = h @ p["q"].T, h @ p["k"].T, h @ p["v"].T
-    q, k, v = short_conv(q, p["q.conv"]), short_conv(k, p["k.conv"]), short_conv(v, p["v.conv"])
+    if "q.conv" in p:
+        q, k, v = short_conv(q, p["q.conv"]), short_conv(k, p["k.conv"]), short_conv(v, p["v.conv"])
     q, k, v = q.view(T, H, D), k.view(T, G, D), v.view(T, G, V)
     q = rms(q, eps) * p["q.norm"]
     k = rms(k, eps) * p["k.norm"]
     pos = torch.arange(pos0, pos0 + T)
-    q = rotate_partial(q, pos, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_partial(k, pos, m["rot"]["dims"], m["rot"]["base"])
-    cap, size, keep = m["softcap"], m["mask"]["size"], m["mask"]["keep_first"]
-    out = torch.zeros(T, H, V, dtype=F)
-    for hd in range(H):
-        g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].T) * m["scale"]
-        s = cap * torch.tanh(s / cap)
-        mask = torch.tensor([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
-        e = torch.where(mask, torch.exp(s), torch.zeros_like(s))
-        out[:, hd] = (e / (1.0 + e.sum(-1, keepdim=True))) @ v[:, g]
+    if m.get("rot") and m["rot"]["dims"]:
+        q = rotate_partial(q, pos, m["rot"]["dims"], m["rot"]["base"])
+        k = rotate_partial(k, pos, m["rot"]["dims"], m["rot"]["base"])
+    mask = m.get("mask") or {}
+    out = attention_core(q, k, v, m["scale"], mask.get("size"), mask.get("keep_first", 0), m.get("softcap") or None, pos0)
     return out.reshape(T, H * V) @ p["o"].T
 
 
@@ -135,6 +147,8 @@ def moe_ff(h, p, m):
         for j in range(r["top"]):
             e = int(idx[t, j])
             out[t] += w[t, j] * expert(h[t:t + 1], p[f"e{e}.gate"], p[f"e{e}.up"], p[f"e{e}.down"])[0]
+    if "shared.gate" not in p:
+        return out
     sh = expert(h, p["shared.gate"], p["shared.up"], p["shared.down"])
     return out + sh * torch.sigmoid(h @ p["shared.sg"].T)
 
@@ -166,3 +180,19 @@ def forward(config, tensors, tokens, layers_out=None):
             layers_out.append(x.clone())
     x = norm_one_plus(x, tensors["final.norm"], eps)
     return x @ tensors["head"].T
+
+
+def read_model(folder):
+    """config.json as a dict and every tensor of model.safetensors in float64."""
+    import json
+    import os
+
+    from safetensors import safe_open
+
+    with open(os.path.join(folder, "config.json")) as f:
+        config = json.load(f)
+    tensors = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), "pt") as f:
+        for k in f.keys():
+            tensors[k] = f.get_tensor(k).to(F)
+    return config, tensors
