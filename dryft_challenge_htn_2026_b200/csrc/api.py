@@ -749,7 +749,7 @@ def masked_tc_takes(q, out, gate, head_dim, v_head_dim):
 
 
 def attention_masked_prefill_tc(q, out, gate, out_scale, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads,
-                                n_kv_heads, head_dim, window, chunk, scale, r1=None, r2=None, sink=None):
+                                n_kv_heads, head_dim, window, chunk, scale, r1=None, r2=None, sink=None, softcap=None, keep_first=0):
     """``attention_masked`` for ragged query portions on tcgen05 tensor cores (bfloat16, equal head sizes of
     64 or 128): the masked build of ``attention_prefill_tc``'s kernel. ``tiles`` lists 128-row tiles."""
     global _tc_err
@@ -772,8 +772,9 @@ def attention_masked_prefill_tc(q, out, gate, out_scale, k_store, v_store, tiles
                                               _p(k_store), _p(v_store), c_longlong(q.shape[0]), c_longlong(k_store.shape[0]),
                                               _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0), _p(page_table),
                                               page_table.shape[1], n_heads, n_kv_heads, int(window or 0), int(chunk or 0),
-                                              c_float(scale), _p(r1), _p(r2), _p(sink), _p(_tc_err), _p(sched),
-                                              c_void_p(stream)), "attention_masked_prefill_tc")
+                                              c_float(scale), _p(r1), _p(r2), _p(sink), c_float(softcap or 0.0),
+                                              int(keep_first or 0), _p(_tc_err), _p(sched), c_void_p(stream)),
+           "attention_masked_prefill_tc")
 
 
 def masked_decode_streams(q, out, gate, head_dim, v_head_dim):
@@ -795,7 +796,8 @@ def masked_decode_splits(n_seq, n_kv_heads, group, table_pages, window, chunk):
 
 
 def attention_decode_masked_bf16(q, out, gate, out_scale, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads,
-                                 head_dim, window, chunk, scale, nsplit, ws_acc, ws_ml, r1=None, r2=None, sink=None):
+                                 head_dim, window, chunk, scale, nsplit, ws_acc, ws_ml, r1=None, r2=None, sink=None,
+                                 softcap=None, keep_first=0):
     """``attention_decode_bf16`` in its masked build: one query token per sequence over its cached keys inside
     its chunk and window, with the distance bias in the scores and the sink, the gate and ``out_scale`` in the
     merge. q, gate and out may be rows of wider matrices. Scratch as ``attention_decode_ws``."""
@@ -815,7 +817,8 @@ def attention_decode_masked_bf16(q, out, gate, out_scale, k_store, v_store, row_
                                                c_longlong(gate.stride(0) if gate is not None else 0), c_float(out_scale),
                                                _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store), _p(row_pos), _p(page_table),
                                                page_table.shape[1], n_seq, n_heads, n_kv_heads, int(window or 0),
-                                               int(chunk or 0), c_float(scale), _p(r1), _p(r2), _p(sink), nsplit, _stream()),
+                                               int(chunk or 0), c_float(scale), _p(r1), _p(r2), _p(sink), c_float(softcap or 0.0),
+                                               int(keep_first or 0), nsplit, _stream()),
            "attention_decode_masked_bf16", 2)
 
 
@@ -1099,3 +1102,42 @@ def moe_down_rows(mid, w_down, idx, wt, shared, shared_gate, out):
     lib = _lib("moe.cu")
     _check(lib, lib.dk_moe_down_rows(_dt(mid), _p(mid), _p(w_down), _p(idx), _p(wt), _p(shared), _p(shared_gate), _p(out), W, ff,
                                      top, T, _stream()), "moe_down_rows")
+
+
+MOE_TILE_ROWS = 64
+
+
+def moe_tiles_take(x, expert_ff):
+    """Whether a step's routed experts run as tiles on the tensor cores: bfloat16, more than 32 tokens, inner
+    sizes (width and expert size) that are multiples of 32."""
+    return x.dtype == torch.bfloat16 and x.shape[0] > 32 and x.shape[1] % 32 == 0 and expert_ff % 32 == 0
+
+
+def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, act=0, scratch=None):
+    """The routed experts for many tokens: pairs sorted by expert on the device, tiles of 64 pairs as matrix
+    products on mma.sync tensor cores (gate/up with the activation, then down), then the weighted sum per token
+    plus shared_gate * shared. ``scratch(key, make)``: where buffers that outlive the call may be kept."""
+    _need(x, "x", torch.bfloat16, 2), _need(w_gate_up, "w_gate_up", torch.bfloat16, 3), _need(w_down, "w_down", torch.bfloat16, 3)
+    _need(idx, "idx", torch.int32, 2), _need(wt, "wt", torch.float32, 2), _need(shared, "shared", torch.bfloat16, 2)
+    _need(shared_gate, "shared_gate", torch.float32, 1), _need(out, "out", torch.bfloat16, 2)
+    T, W = x.shape
+    top = idx.shape[1]
+    E, ff = w_down.shape[0], w_down.shape[2]
+    if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape[1] != W or idx.shape[0] != T or wt.shape != idx.shape or \
+            out.shape != (T, W) or W % 32 or ff % 32 or E > MOE_MAX_EXPERTS or (shared is not None and shared.shape != (T, W)):
+        raise KernelError("moe_experts_tiles: shapes do not match (inner sizes in steps of 32)")
+    P = T * top
+    max_tiles = (P + MOE_TILE_ROWS - 1) // MOE_TILE_ROWS + E
+    dev = x.device
+
+    def make():
+        return (torch.empty(P, dtype=torch.int32, device=dev), torch.empty(P, dtype=torch.int32, device=dev),
+                torch.empty((max_tiles, 3), dtype=torch.int32, device=dev), torch.empty((P, ff), dtype=torch.bfloat16, device=dev),
+                torch.empty((P, W), dtype=torch.bfloat16, device=dev))
+    perm, inv, tiles, mid, y = scratch(("moe_tiles", T, top, E, ff, W), make) if scratch is not None else make()
+    lib = _lib("moe_tiles.cu")
+    _check(lib, lib.dk_moe_sort(_p(idx), P, E, _p(perm), _p(inv), _p(tiles), max_tiles, _stream()), "moe_sort")
+    _check(lib, lib.dk_moe_up_tiles(_p(x), _p(w_gate_up), _p(tiles), max_tiles, _p(perm), top, _p(mid), ff, W, int(act), _stream()),
+           "moe_up_tiles")
+    _check(lib, lib.dk_moe_down_tiles(_p(mid), _p(w_down), _p(tiles), max_tiles, _p(y), W, ff, _stream()), "moe_down_tiles")
+    _check(lib, lib.dk_moe_sum(_p(y), _p(inv), _p(wt), _p(shared), _p(shared_gate), _p(out), T, W, top, _stream()), "moe_sum")

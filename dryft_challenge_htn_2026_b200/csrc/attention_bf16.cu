@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
                    const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2
 #if DK_MASKED
-                   , long long ldq, int chunk, const float* __restrict__ r1, const float* __restrict__ r2
+                   , long long ldq, int chunk, const float* __restrict__ r1, const float* __restrict__ r2, int keep_first,
+                   float cap_l2, float scale_over_cap
 #endif
                    ) {
     extern __shared__ __align__(16) bf16 smem[];
@@ -145,14 +146,22 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
 #if DK_MASKED
     int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
     if (chunk > 0 && pos >= 0) key_lo = max(key_lo, pos / chunk * chunk);
+    if (keep_first >= key_lo) key_lo = 0;            // the kept first tokens reach the window: all up to pos is in sight
+    const int kf = key_lo > 0 ? keep_first : 0;      // kept first tokens that lie apart from the window
 #else
     const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int kf = 0;
 #endif
     const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
-    const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
-    const int jt0 = t_lo + split * per, jt1 = pos >= 0 ? min(t_hi + 1, jt0 + per) : jt0;  // [jt0, jt1)
+    // the pages this row reads, numbered in one run: the kept tokens' pages before the window's first, then the window's
+    const int kp = min((kf + DK_PAGE - 1) / DK_PAGE, t_lo);
+    const int n_pages = kp + t_hi - t_lo + 1;
+    const int per = (n_pages + nsplit - 1) / nsplit;
+    const int jt0 = split * per, jt1 = pos >= 0 ? min(n_pages, jt0 + per) : jt0;  // [jt0, jt1) of that run
+    const int t_new = n_pages - 1;                   // the newest token's page
     const uint64_t stream_once = l2_evict_first();
-    auto fetch = [&](int jt, int slot) {
+    auto fetch = [&](int u, int slot) {
+        const int jt = u < kp ? u : t_lo + u - kp;
         const size_t off = kv_offset(pt[jt], nkv, kvh, warp * 16, HD);
         bf16* dst = ring + slot * CHUNK;
         for (int c = lane; c < 16 * CPR; c += 32) {
@@ -162,7 +171,7 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
         }
     };
     int issued = 0;                           // chunks requested so far; chunk i is commit group i
-    for (; issued < D && jt0 + issued < min(jt1, t_hi); issued++) {
+    for (; issued < D && jt0 + issued < min(jt1, t_new); issued++) {
         fetch(jt0 + issued, issued);
         cp_async_commit();
     }
@@ -189,24 +198,32 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
             if (g + 8 < heads_here) bias_rows[1] = r1[head0 + g + 8], bias_rows[3] = r2[head0 + g + 8];
         }
         const float* bias = r1 != nullptr ? bias_rows : nullptr;
+        const float cap_pair[2] = {cap_l2, scale_over_cap};
+        const float* cap = cap_l2 > 0.f ? cap_pair : nullptr;
+        const int klo[2] = {0, 0}, khi[2] = {kf - 1, kf - 1};
 #else
         const bf16* qb = q + ((size_t)b * nh + head0) * HD;
         const float* bias = nullptr;
+        const float* cap = nullptr;
 #endif
         load_q_frags(qf, g < heads_here ? qb + (size_t)g * HD : nullptr,
                      g + 8 < heads_here ? qb + (size_t)(g + 8) * HD : nullptr);
         const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
-        for (int jt = jt0; jt < jt1; jt++) {
-            const int slot = (jt - jt0) % D;
-            cp_async_wait<D - 1>();           // this warp's chunk jt has landed
+        for (int u = jt0; u < jt1; u++) {
+            const int slot = (u - jt0) % D;
+            cp_async_wait<D - 1>();           // this warp's chunk u has landed
             __syncwarp();
+            const int jt = u < kp ? u : t_lo + u - kp;
             const int key0 = jt * DK_PAGE + warp * 16;
-            if (key0 <= pos && key0 + 15 >= key_lo) {
-                const bf16* Ks = ring + slot * CHUNK;
-                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, lo, hi, sl2, m, l, acc, bias);
-            }
+            const bf16* Ks = ring + slot * CHUNK;
+            if (u >= kp && key0 <= pos && key0 + 15 >= key_lo)
+                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, lo, hi, sl2, m, l, acc, bias, cap);
+#if DK_MASKED
+            if (key0 < kf)                    // kept first tokens, in a page of their own or below the window in its first page
+                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, klo, khi, sl2, m, l, acc, bias, cap);
+#endif
             __syncwarp();                     // every lane is done reading the slot before it is refilled
-            if (jt + D < jt1) fetch(jt + D, slot);
+            if (u + D < jt1) fetch(u + D, slot);
             cp_async_commit();
         }
     }
@@ -384,21 +401,22 @@ DK_EXPORT int dk_attn_decode_masked_bf16(const void* q, long long ldq, void* out
                                          float out_scale, float* ws_acc, float* ws_ml, const void* k_store, const void* v_store,
                                          const int* row_pos, const int* page_table, int pt_stride, int n_seq, int nh, int nkv,
                                          int window, int chunk, float scale, const float* r1, const float* r2,
-                                         const float* sink, int nsplit, cudaStream_t st) {
+                                         const float* sink, float softcap, int keep_first, int nsplit, cudaStream_t st) {
     if (nh % nkv != 0 || nsplit < 1 || nsplit > 32 || ws_acc == nullptr || ws_ml == nullptr || ldq % 2 || ldo % 4 ||
         (gate && ldg % 4) || ((uintptr_t)out | (uintptr_t)gate) % 8 != 0 || (uintptr_t)q % 4 != 0)
         return (int)cudaErrorInvalidValue;
     int e = ensure_smem_attr();
     if (e) return e;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
+    const float cap_l2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f, soc = softcap > 0.f ? scale / softcap : 0.f;
     if (decode_ring_depth((long long)nsplit * nkv * mtiles * n_seq) == 3)
         e = dk_launch(attn_decode_kernel<3>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(3), st, (const bf16*)q,
                       ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv,
-                      window, scale * 1.4426950408889634f, ldq, chunk, r1, r2);
+                      window, scale * 1.4426950408889634f, ldq, chunk, r1, r2, keep_first, cap_l2, soc);
     else
         e = dk_launch(attn_decode_kernel<2>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(2), st, (const bf16*)q,
                       ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv,
-                      window, scale * 1.4426950408889634f, ldq, chunk, r1, r2);
+                      window, scale * 1.4426950408889634f, ldq, chunk, r1, r2, keep_first, cap_l2, soc);
     if (e) return e;
     return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
                      (const float*)ws_ml, (bf16*)out, 4 * nsplit, n_seq * nh, nh, ldo, (const bf16*)gate, ldg, out_scale, sink);

@@ -64,10 +64,13 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[HD / 16][4], const b
 // Row r (0: lane group g, 1: g+8) may see keys with lo[r] <= absolute position <= hi[r].
 // Scores are kept in the log2 domain: sl2 = scale * log2(e). ``bias`` (or null) = {b1 of row 0, b1 of row 1, b2 of
 // row 0, b2 of row 1}: a logarithmic distance bias b1 * log2(1 + b2 * (hi[r] - key)) is taken off row r's scores.
+// ``cap`` (or null) = {cap * log2(e), scale / cap}: the score becomes cap * tanh(score / cap), with the tanh from one
+// exponential and one division (1 - 2 / (e^(2y) + 1)), before the bias.
 template <int NKEYS>
 __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[HD / 16][4], const bf16* Ks, const bf16* Vs, int key0,
                                             const int (&lo)[2], const int (&hi)[2], float sl2, float (&m)[2],
-                                            float (&l)[2], float (&acc)[HD / 8][4], const float* bias = nullptr) {
+                                            float (&l)[2], float (&acc)[HD / 8][4], const float* bias = nullptr,
+                                            const float* cap = nullptr) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NKEYS / 8][4];
 #pragma unroll
@@ -92,6 +95,8 @@ __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[HD / 16][4], co
             float v = -INFINITY;
             if (key >= lo[r] && key <= hi[r]) {
                 v = s[nt][c] * sl2;
+                if (cap != nullptr)
+                    v = cap[0] * (1.f - __fdividef(2.f, exp2f(s[nt][c] * cap[1] * 2.8853900817779268f) + 1.f));
                 if (bias != nullptr) v -= bias[r] * __log2f(fmaf(bias[2 + r], (float)(hi[r] - key), 1.f));
             }
             s[nt][c] = v;

@@ -237,7 +237,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* seq_pos0, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
                        int* err, int* sched
 #if DK_MASKED
-                       , long long ldo, const bf16* gate, long long ldg, float out_scale, int chunk,
+                       , long long ldo, const bf16* gate, long long ldg, float out_scale, int chunk, int keep_first,
+                       float cap_l2, float scale_over_cap,
                        const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink
 #endif
                        ) {
@@ -276,7 +277,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // What an item (tile, head) is, as every role needs it.
     struct Item {
-        int h, kvh, rows_here, flat0, min_pos, max_pos, pos0, q0, blk_lo, n_blk;
+        int h, kvh, rows_here, flat0, min_pos, max_pos, pos0, q0, blk_lo, n_blk, n_kept;
         const int* pt;
     };
     auto item_of = [&](int item) {
@@ -295,6 +296,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         it.blk_lo = window > 0 ? max(0, it.min_pos - window + 1) / BN : 0;
 #endif
         it.n_blk = it.max_pos / BN - it.blk_lo + 1;
+        it.n_kept = 0;
+#if DK_MASKED
+        // kept first tokens that the window (or chunk) has left behind: their key blocks are the item's first steps
+        it.n_kept = min((keep_first + BN - 1) / BN, it.blk_lo);
+        it.n_blk += it.n_kept;
+#endif
         return it;
     };
     // loader only; t0 = the item's first step
@@ -302,7 +309,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t b = (t0 + j) & 1;
         mbar_expect_tx(bar + b, KV_BYTES);
         for (int pg = 0; pg < PAGES; pg++) {
-            int page = it.pt[min((it.blk_lo + j) * PAGES + pg, pt_stride - 1)];
+            const int blk = j < it.n_kept ? j : it.blk_lo + j - it.n_kept;
+            int page = it.pt[min(blk * PAGES + pg, pt_stride - 1)];
             if (page < 0) page = 0;                         // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
             const int row = (page * nkv + it.kvh) * DK_PAGE;
             for (int hh = 0; hh < HALVES; hh++)
@@ -424,7 +432,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = true;
         for (int i = 0; i < n_blk && ok; i++) {
             const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
-            const int key0 = (blk_lo + i) * BN;
+            const int key0 = (i < cur.n_kept ? i : blk_lo + i - cur.n_kept) * BN;
 #if DK_MASKED
             {   // this step's bias table, while S is still on its way (zeros without a bias)
                 float* tw = bias_tab + (t & 1) * BIAS_TAB;
@@ -447,10 +455,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // scores leave this loop in the log2 domain with the distance bias taken off: the bias of row lane, key j
             // of the step sits at tab[lane + 63 - j] (distance = first distance of the warp in this step + that index)
             const float* tab = bias_tab + (t & 1) * BIAS_TAB + lane + (BN - 1);
+            if (cap_l2 > 0.f) {
+                // capped scores: cap * tanh(score / cap), here times log2(e); tanh(y) = 1 - 2 / (e^(2y) + 1) from one
+                // exponential and one fast division (the hardware's own tanh is good to 11 bits only, which a cap of
+                // some tens of units turns into percents of a weight)
+#pragma unroll
+                for (int j = 0; j < CPT; j++) {
+                    const float e = ex2(__uint_as_float(v[j]) * scale_over_cap * 2.8853900817779268f);
+                    v[j] = __float_as_uint(cap_l2 * (1.f - __fdividef(2.f, e + 1.f)));
+                }
+            }
+            const float sl = cap_l2 > 0.f ? 1.f : sl2;
             if (open) {
 #pragma unroll
                 for (int j = 0; j < CPT; j++) {
-                    const float x = fmaf(__uint_as_float(v[j]), sl2, -tab[-j]);
+                    const float x = fmaf(__uint_as_float(v[j]), sl, -tab[-j]);
                     v[j] = __float_as_uint(x);
                     mx4[j & 3] = fmaxf(mx4[j & 3], x);
                 }
@@ -458,8 +477,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int j = 0; j < CPT; j++) {
                     const int key = key0 + j;
-                    float x = fmaf(__uint_as_float(v[j]), sl2, -tab[-j]);
-                    x = (valid && key <= qpos && key >= key_lo) ? x : -INFINITY;
+                    float x = fmaf(__uint_as_float(v[j]), sl, -tab[-j]);
+                    x = (valid && key <= qpos && (key >= key_lo || key < keep_first)) ? x : -INFINITY;
                     v[j] = __float_as_uint(x);
                     mx4[j & 3] = fmaxf(mx4[j & 3], x);
                 }
@@ -660,8 +679,8 @@ DK_EXPORT int dk_attn_prefill_tc_masked(const void* q, long long ldq, void* out,
                                         float out_scale, const void* k_store, const void* v_store, long long n_tok,
                                         long long n_pages, const int* tiles, int n_tiles, const int* cu_q, const int* seq_pos0,
                                         const int* page_table, int pt_stride, int nh, int nkv, int window, int chunk, float scale,
-                                        const float* r1, const float* r2, const float* sink, int* err, int* sched,
-                                        cudaStream_t st) {
+                                        const float* r1, const float* r2, const float* sink, float softcap, int keep_first,
+                                        int* err, int* sched, cudaStream_t st) {
     if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1 || ldq % 8 || ldo % 8 || (gate && ldg % 8) ||
         ((uintptr_t)q | (uintptr_t)out | (uintptr_t)gate) % 16 != 0)
         return (int)cudaErrorInvalidValue;
@@ -686,6 +705,7 @@ DK_EXPORT int dk_attn_prefill_tc_masked(const void* q, long long ldq, void* out,
     const int blocks = (int)(n_items < slots ? n_items : slots);
     return dk_launch(attn_prefill_tc_kernel, dim3(blocks), dim3(THREADS), smem, st, mq, mk, mv, (bf16*)out, tiles, (int)n_items,
                      cu_q, seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err, sched, ldo,
-                     (const bf16*)gate, ldg, out_scale, chunk, r1, r2, sink);
+                     (const bf16*)gate, ldg, out_scale, chunk, keep_first, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f,
+                     softcap > 0.f ? scale / softcap : 0.f, r1, r2, sink);
 }
 #endif

@@ -1,0 +1,203 @@
+// The routed experts of a mixture of experts for many tokens at once, bfloat16, on mma.sync tensor cores.
+//
+// The (token, chosen expert) pairs are put in the order of their experts on the device (one block counts,
+// scans and scatters; nothing goes through the host, so the step can be captured as a graph), cut into tiles
+// of 64 pairs of one expert, and every tile is a small matrix product against that expert's matrices:
+//   up:    mid[r] = act(W_gate[e] x_r) * (W_up[e] x_r)      rows gathered by token, both products in one pass
+//   down:  y[r]   = W_down[e] mid[r]
+//   sum:   out[t] = sum_j weight[t][j] * y[place of pair (t, j)] + gate[t] * shared[t]
+// A row's sums run over its own elements in a fixed order, so a result does not depend on which other pairs
+// share its tile. Grids are sized for the most tiles the pairs can make (pairs / 64 + experts); blocks
+// beyond the tiles that exist leave at once.
+#include "common.cuh"
+
+#define MT_ROWS 64      // pairs a tile
+#define MT_COLS 64      // output columns a block
+#define MT_KC 32        // inner elements a stage
+#define MT_STR (MT_KC + 8)
+
+__device__ __forceinline__ void mt_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mt_ldsm(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mt_cp16(bf16* smem, const bf16* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void mt_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void mt_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One block. idx [P] = expert of every pair. Leaves perm [P] (pairs in expert order), inv [P] (a pair's place in
+// that order) and for every tile its expert, first place and row count in tiles [max_tiles][3] (rows 0: no tile).
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* idx, int P, int E, int* perm, int* inv, int* tiles, int max_tiles) {
+    __shared__ int cnt[256], off[257], tbase[257];
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&cnt[idx[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        off[0] = tbase[0] = 0;
+        for (int e = 0; e < E; e++) {
+            off[e + 1] = off[e] + cnt[e];
+            tbase[e + 1] = tbase[e] + (cnt[e] + MT_ROWS - 1) / MT_ROWS;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        for (int k = 0; tbase[e] + k < tbase[e + 1]; k++) {
+            int* t = tiles + 3 * (tbase[e] + k);
+            t[0] = e, t[1] = off[e] + k * MT_ROWS, t[2] = min(MT_ROWS, cnt[e] - k * MT_ROWS);
+        }
+    }
+    for (int t = tbase[E] + threadIdx.x; t < max_tiles; t += blockDim.x) tiles[3 * t] = 0, tiles[3 * t + 1] = 0, tiles[3 * t + 2] = 0;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = idx[p];
+        const int at = off[e] + atomicAdd(&cnt[e], 1);
+        perm[at] = p;
+        inv[p] = at;
+    }
+}
+
+// Block (tile, 64 columns of the output). GATED: B is an expert's [gate rows; up rows] (2 * N rows of K), the
+// output act(gate) * up; A rows are gathered (row r of the tile is token perm[first + r] / top of x). Otherwise B is
+// the expert's [N rows of K] and A the rows first + r of a dense matrix. K % 32 == 0; rows on 16-byte boundaries.
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* tiles, const int* perm, int top, bf16* out,
+                        int N, int K, int act) {
+    __shared__ __align__(16) bf16 As[2][MT_ROWS * MT_STR];
+    __shared__ __align__(16) bf16 Bs[2][(GATED ? 2 : 1) * MT_COLS * MT_STR];
+    __shared__ int arow[MT_ROWS];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int* tl = tiles + 3 * blockIdx.x;
+    const int rows = tl[2];
+    if (rows == 0) return;
+    const int e = tl[0], first = tl[1];
+    const int n0 = blockIdx.y * MT_COLS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < MT_ROWS) arow[tid] = tid < rows ? (GATED ? perm[first + tid] / top : first + tid) : -1;
+    for (int i = tid; i < 2 * MT_ROWS * MT_STR / 8; i += 128) reinterpret_cast<uint4*>(&As[0][0])[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < 2 * (GATED ? 2 : 1) * MT_COLS * MT_STR / 8; i += 128)
+        reinterpret_cast<uint4*>(&Bs[0][0])[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    const bf16* Be = B + (size_t)e * (GATED ? 2 : 1) * N * K;
+    auto load = [&](int kc, int buf) {
+        const int k0 = kc * MT_KC;
+        for (int i = tid; i < MT_ROWS * 4; i += 128) {             // 4 pieces of 8 elements a row
+            const int r = i >> 2, c = (i & 3) * 8;
+            if (arow[r] >= 0) mt_cp16(&As[buf][r * MT_STR + c], A + (size_t)arow[r] * K + k0 + c);
+        }
+        for (int i = tid; i < (GATED ? 2 : 1) * MT_COLS * 4; i += 128) {
+            const int r = i >> 2, c = (i & 3) * 8;
+            const int n = n0 + (r % MT_COLS);
+            if (n < N) mt_cp16(&Bs[buf][r * MT_STR + c], Be + ((size_t)(r / MT_COLS) * N + n) * K + k0 + c);
+        }
+        mt_commit();
+    };
+    float accg[8][4], accu[GATED ? 8 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) accg[i][0] = accg[i][1] = accg[i][2] = accg[i][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < (GATED ? 8 : 1); i++) accu[i][0] = accu[i][1] = accu[i][2] = accu[i][3] = 0.f;
+    const int nk = K / MT_KC;
+    load(0, 0);
+    const int j = lane >> 3;
+    for (int kc = 0; kc < nk; kc++) {
+        const int buf = kc & 1;
+        if (kc + 1 < nk) {
+            load(kc + 1, buf ^ 1);
+            mt_wait<1>();
+        } else {
+            mt_wait<0>();
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MT_KC / 16; kk++) {
+            uint32_t a[4];
+            mt_ldsm(a, &As[buf][(warp * 16 + (lane & 15)) * MT_STR + kk * 16 + 8 * (lane >> 4)]);
+#pragma unroll
+            for (int np = 0; np < 4; np++) {
+                uint32_t b[4];
+                mt_ldsm(b, &Bs[buf][(np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1)]);
+                mt_mma(accg[2 * np], a, b[0], b[1]);
+                mt_mma(accg[2 * np + 1], a, b[2], b[3]);
+                if (GATED) {
+                    mt_ldsm(b, &Bs[buf][(MT_COLS + np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1)]);
+                    mt_mma(accu[2 * np], a, b[0], b[1]);
+                    mt_mma(accu[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int r = warp * 16 + g + 8 * (c >> 1), n = n0 + nt * 8 + 2 * t + (c & 1);
+            if (r < rows && n < N) {
+                float v = accg[nt][c];
+                if (GATED) {
+                    const float u = accu[nt][c];
+                    v = (act == 1 ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                                  : v / (1.f + expf(-v))) * u;
+                }
+                out[(size_t)(first + r) * N + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+// out[t][c] = sum_j wt[t][j] * y[inv[t * top + j]][c] + sgate[t] * shared[t][c]
+__global__ void moe_sum_kernel(const bf16* y, const int* inv, const float* wt, const bf16* shared, const float* sgate, bf16* out,
+                               int W, int top) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; j++) acc = fmaf(wt[t * top + j], __bfloat162float(y[(size_t)inv[t * top + j] * W + c]), acc);
+        if (shared != nullptr) acc = fmaf(sgate ? sgate[t] : 1.f, __bfloat162float(shared[t * W + c]), acc);
+        out[t * W + c] = __float2bfloat16_rn(acc);
+    }
+}
+
+DK_EXPORT int dk_moe_sort(const int* idx, int P, int E, int* perm, int* inv, int* tiles, int max_tiles, cudaStream_t st) {
+    if (E < 1 || E > 256 || max_tiles < (P + MT_ROWS - 1) / MT_ROWS + E - 1) return (int)cudaErrorInvalidValue;
+    return dk_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, st, idx, P, E, perm, inv, tiles, max_tiles);
+}
+
+DK_EXPORT int dk_moe_up_tiles(const void* x, const void* wgu, const int* tiles, int max_tiles, const int* perm, int top, void* mid,
+                              int ff, int W, int act, cudaStream_t st) {
+    if (W % MT_KC || ((uintptr_t)x | (uintptr_t)wgu) % 16) return (int)cudaErrorInvalidValue;
+    return dk_launch(moe_tile_product_kernel<true>, dim3(max_tiles, (ff + MT_COLS - 1) / MT_COLS), dim3(128), 0, st, (const bf16*)x,
+                     (const bf16*)wgu, tiles, perm, top, (bf16*)mid, ff, W, act);
+}
+
+DK_EXPORT int dk_moe_down_tiles(const void* mid, const void* wd, const int* tiles, int max_tiles, void* y, int W, int ff,
+                                cudaStream_t st) {
+    if (ff % MT_KC || ((uintptr_t)mid | (uintptr_t)wd) % 16) return (int)cudaErrorInvalidValue;
+    return dk_launch(moe_tile_product_kernel<false>, dim3(max_tiles, (W + MT_COLS - 1) / MT_COLS), dim3(128), 0, st, (const bf16*)mid,
+                     (const bf16*)wd, tiles, (const int*)nullptr, 1, (bf16*)y, W, ff, 0);
+}
+
+DK_EXPORT int dk_moe_sum(const void* y, const int* inv, const float* wt, const void* shared, const float* sgate, void* out,
+                         int n_tok, int W, int top, cudaStream_t st) {
+    return dk_launch(moe_sum_kernel, dim3(n_tok), dim3(W >= 1024 ? 256 : 128), 0, st, (const bf16*)y, inv, wt, (const bf16*)shared,
+                     sgate, (bf16*)out, W, top);
+}

@@ -56,8 +56,10 @@ class MaskedAttention(Part):
         self.max_positions = 0
         # the tensor-core kernels take bfloat16 with head sizes in steps of 16; everything else (float32, odd
         # head sizes) runs on the float32-arithmetic kernel, which serves every phase
-        self.tensor_core = rt.dtype == torch.bfloat16 and api.masked_bf16_takes(s.head_dim, s.v_head_dim) \
-            and s.softcap is None and not s.keep_first
+        self.tensor_core = rt.dtype == torch.bfloat16 and api.masked_bf16_takes(s.head_dim, s.v_head_dim)
+        # a cap on the scores and kept first tokens are options of the float32-arithmetic kernel, of the tcgen05 prompt
+        # kernel and of the split single-token kernel (equal head sizes); the mma.sync kernels for other sizes lack them
+        self.plain_options = s.softcap is None and not s.keep_first
         self.tiles = QueryTiles(api.MASKED_TILE_ROWS) if self.tensor_core else None
         # equal head sizes of 64 or 128: prompts run on the tcgen05 kernel (its masked build), in tiles of 128 queries
         self.tc_tiles = QueryTiles(api.TC_TILE_ROWS) if self.tensor_core and s.head_dim == s.v_head_dim \
@@ -161,9 +163,10 @@ class MaskedAttention(Part):
                                         lambda: api.attention_decode_ws(ctx.n_seq, s.num_heads, s.head_dim, nsplit, self.rt.device))
             return api.attention_decode_masked_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, table, s.num_heads,
                                                     s.num_kv_heads, s.head_dim, s.window, s.chunk, s.scale, nsplit, ws_acc,
-                                                    ws_ml, self.r1, self.r2, self.sink)
+                                                    ws_ml, self.r1, self.r2, self.sink, s.softcap, s.keep_first)
         span = api.masked_decode_span(s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.chunk, table.shape[1], ctx.n_tok) \
-            if self.tensor_core and ctx.is_decode and all(t is None or t.stride(0) % 2 == 0 for t in (q, mid, gate)) else None
+            if self.tensor_core and self.plain_options and ctx.is_decode \
+            and all(t is None or t.stride(0) % 2 == 0 for t in (q, mid, gate)) else None
         if span is not None:      # single tokens: the kernel stores each token's key and value itself
             ws = None
             if span[1] > 1:
@@ -176,9 +179,9 @@ class MaskedAttention(Part):
         if self.tc_tiles is not None and not ctx.is_decode and api.masked_tc_takes(q, mid, gate, s.head_dim, s.v_head_dim):
             return api.attention_masked_prefill_tc(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tc_tiles.key], ctx.cu_q,
                                                    ctx.seq_pos0, table, s.num_heads, s.num_kv_heads, s.head_dim, s.window,
-                                                   s.chunk, s.scale, self.r1, self.r2, self.sink)
+                                                   s.chunk, s.scale, self.r1, self.r2, self.sink, s.softcap, s.keep_first)
         even = all(t is None or (t.stride(0) % 2 == 0 and t.data_ptr() % 4 == 0) for t in (q, mid, gate))
-        if self.tensor_core and not ctx.is_decode and even:
+        if self.tensor_core and self.plain_options and not ctx.is_decode and even:
             return api.attention_masked_prefill_bf16(q, mid, gate, scale, kv.k, kv.v, ctx.plans[self.tiles.key], ctx.cu_q,
                                                      ctx.seq_pos0, table, *sizes, self.r1, self.r2, self.sink)
         api.attention_masked(q, mid, gate, scale, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, *sizes, self.r1, self.r2,

@@ -2,7 +2,9 @@
 
 forward = router kernel (sigmoid scores, choice by score + correction among the best groups, weights from the
 scores alone; also the shared expert's gate) -> the chosen experts' gate/up products with the activation ->
-their down products, weighted and summed per token, plus gate * shared expert. The experts' matrices are
+their down products, weighted and summed per token, plus gate * shared expert. Steps of many tokens in bfloat16
+sort the (token, expert) pairs by expert on the device and run tiles of one expert on the tensor cores; single
+tokens, float32 and odd sizes run a warp per output, each pair reading its expert's rows once. The experts' matrices are
 stacked [experts, rows, inner] when they are bound, so that a kernel finds an expert's rows by its number.
 """
 import torch
@@ -75,9 +77,15 @@ class RoutedMLP(Part):
         shared = None
         if s.shared_ff is not None:
             shared = linear(linear(a, self.w_shared_gu, SILU), self.w_shared_down)
+        out = torch.empty((T, s.hidden_size), dtype=self.rt.dtype, device=dev)
+        if api.moe_tiles_take(a, s.expert_ff):
+            # many tokens: the pairs sorted by expert, tiles of one expert on the tensor cores
+            api.moe_experts_tiles(a, self.w_gate_up, self.w_down, idx, wt, shared, sgate, out, _ACTS[s.activation],
+                                  ctx.scratch if ctx is not None else None)
+            return out
+        # few tokens (a pair reads its expert's matrices once), float32, or sizes the tiles do not take
         mid = torch.empty((T * s.top, s.expert_ff), dtype=self.rt.dtype, device=dev)
         api.moe_up_rows(a, self.w_gate_up, idx, mid, _ACTS[s.activation])
-        out = torch.empty((T, s.hidden_size), dtype=self.rt.dtype, device=dev)
         api.moe_down_rows(mid, self.w_down, idx, wt, shared, sgate, out)
         return out
 
