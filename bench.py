@@ -495,8 +495,164 @@ def kernel_times(torch, dk, pk, heads, kv_heads, rh, chunk):
     return out
 
 
+def pibulix_config(width, heads, kv_heads, ff_qwen, layers, vocab, window):
+    """A Pibulix model of Qwen3's width, head size 128 and layer count: attention layers of Qwen3's head counts (4 taps,
+    half the head rotated, a window that keeps 4 tokens, capped scores) with a dense feed-forward of Qwen3's size, in
+    turn with gated-linear-attention layers of half as many heads whose mixture of 32 experts uses 4 a token, each a
+    quarter of Qwen3's feed-forward (so that a token's feed-forward arithmetic is Qwen3's), plus a shared expert."""
+    hd, gh = 128, heads // 2
+    eff = max(64, ff_qwen // 4 // 64 * 64)
+    att = {"type": "attention",
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": hd, "vdim": hd, "conv": 4, "scale": hd ** -0.5, "softcap": 50.0,
+                     "rot": {"dims": hd // 2, "base": 1e6}, "mask": {"size": window, "keep_first": 4}},
+           "mlp": {"kind": "dense", "ff": ff_qwen}}
+    gla = {"type": "gla", "mixer": {"heads": gh, "dim": hd, "vdim": hd, "tau": 16.0},
+           "mlp": {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": eff},
+                   "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}}
+    return dict(architecture="Pibulix", vocab=vocab, width=width, norm={"eps": 1e-6}, postln_alpha=2.0,
+                layers=[att if i % 2 == 0 else gla for i in range(layers)])
+
+
+def pibulix_kernel_times(torch, dk, pk, width, heads, kv_heads, ff_qwen, window):
+    """The design's own kernels alone, beside Qwen3's like kernels at the same head counts: CUDA events around one launch
+    (or one part's forward), L2 flushed before each (a 256 MB write), median of 5 after 2 untimed."""
+    from dryft_challenge_htn_2026_b200.cache import Cache, KVRequest, StateRequest
+    from dryft_challenge_htn_2026_b200.config.specs import GatedMLPSpec, RoutedMLPSpec
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.engine.batch import build_context
+    from dryft_challenge_htn_2026_b200.parts import Runtime, build_part
+    from dryft_challenge_htn_2026_b200.parts.attention import QueryTiles
+    dev, bf = torch.device("cuda"), torch.bfloat16
+    hd, gh, keep, cap = 128, heads // 2, 4, 50.0
+    eff = max(64, ff_qwen // 4 // 64 * 64)
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+
+    def timed(fn):
+        ts = []
+        for i in range(7):
+            flush.fill_(float(i))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts[2:]) * 1e3        # microseconds
+
+    def flops_rec(us, flops):
+        return {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1), "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}
+
+    def bytes_rec(us, moved):
+        return {"us": round(us, 1), "gbs": round(moved / us / 1e3, 1), "frac_hbm": round(moved / us / 1e3 / pk["hbm_gbs"], 4)}
+
+    out = {}
+    sink = torch.zeros(heads, device=dev)
+    rt = Runtime(dev, bf)
+    moe = build_part(RoutedMLPSpec(width, eff, 32, 4, 4, 2, 2.5, eff), rt)
+    dense = build_part(GatedMLPSpec(width, ff_qwen), rt)
+    g = torch.Generator(device=dev).manual_seed(1)
+    for part in (moe, dense):
+        part.bind({d.name: (torch.randn(d.shape, generator=g, device=dev) * (0.2 if d.init == "wide" else 0.02)).to(
+            torch.float32 if d.keep_float32 else bf) for d in part.param_decls()})
+    scratch = {}
+
+    class Ctx:
+        def scratch(self, key, make):
+            if key not in scratch:
+                scratch[key] = make()
+            return scratch[key]
+    for tokens in (2048, 8192):
+        plans = [QueryTiles(api.TC_TILE_ROWS)]
+        cache = Cache([[KVRequest(kv_heads, hd, window, bf, hd, None, keep)], [KVRequest(kv_heads, hd, None, bf)],
+                       [StateRequest((gh, hd, hd), torch.float32)]], tokens + 64, 2, dev)
+        slot = cache.begin()
+        ctx = build_context(cache, [(slot, [0] * tokens, [])], dev, plans=plans)
+        q = torch.randn(tokens, heads * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        for e in (0, 1):
+            v = cache.views(e)[0]
+            v.k.normal_(), v.v.normal_()
+        m, f, stt = cache.views(0)[0], cache.views(1)[0], cache.views(2)[0].state
+        seen = sum(min(i + 1, window) + min(keep, max(0, i + 1 - window)) for i in range(tokens))
+        us = timed(lambda: api.attention_masked_prefill_tc(q, o, None, 1.0, m.k, m.v, ctx.plans[plans[0].key], ctx.cu_q, ctx.seq_pos0,
+                                                           ctx.tables[m.group], heads, kv_heads, hd, window, None, hd ** -0.5, None, None,
+                                                           sink, cap, keep))
+        out[f"window_attention_prefill_{tokens}"] = flops_rec(us, 4 * heads * hd * seen)
+        us = timed(lambda: api.attention_masked_prefill_tc(q, o, None, 1.0, m.k, m.v, ctx.plans[plans[0].key], ctx.cu_q, ctx.seq_pos0,
+                                                           ctx.tables[m.group], heads, kv_heads, hd, window, None, hd ** -0.5, None, None,
+                                                           sink, None, keep))
+        out[f"window_attention_prefill_without_cap_{tokens}"] = flops_rec(us, 4 * heads * hd * seen)
+        full = tokens * (tokens + 1) // 2
+        us = timed(lambda: api.attention_prefill_tc(q, o, f.k, f.v, ctx.plans[plans[0].key], ctx.cu_q, ctx.seq_pos0, ctx.tables[f.group],
+                                                    heads, kv_heads, hd, None, hd ** -0.5))
+        out[f"qwen3_attention_prefill_{tokens}"] = flops_rec(us, 4 * heads * hd * full)
+        # ---- prompts: gated linear attention; what it must move: q, k, v in, the decay's float32 rows in, float32 o out
+        x = torch.randn(tokens, 3 * gh * hd, device=dev).to(bf)
+        z = torch.randn(tokens, gh * hd, device=dev)
+        zb = torch.zeros(gh * hd, device=dev)
+        lo = torch.empty(tokens, gh * hd, dtype=torch.float32, device=dev)
+        us = timed(lambda: api.gated_linear_attention(x[:, :gh * hd], x[:, gh * hd:2 * gh * hd], x[:, 2 * gh * hd:], lo, stt, ctx.cu_q,
+                                                           ctx.seq_pos0, ctx.seq_slot, z, zb, 16.0, hd ** -0.5, 1, gh, hd, hd))
+        out[f"gated_linear_attention_prefill_{tokens}"] = bytes_rec(us, tokens * gh * hd * (3 * 2 + 4 + 4))
+        # ---- prompts: the routed feed-forward beside Qwen3's dense one (a token's arithmetic is the same but for the shared expert)
+        a = torch.randn(tokens, width, device=dev).to(bf)
+        us = timed(lambda: moe.forward(Ctx(), a))
+        out[f"routed_feed_forward_prefill_{tokens}"] = flops_rec(us, tokens * 5 * 6 * eff * width)
+        us = timed(lambda: dense.forward(None, a))
+        out[f"qwen3_feed_forward_prefill_{tokens}"] = flops_rec(us, tokens * 6 * ff_qwen * width)
+        cache.end(slot)
+        del cache, q, o, x, z, lo, a
+    for batch in (8, 64):
+        # ---- single tokens: every sequence holds 3,000 tokens, of which the window and the kept ones are read
+        context = 3000
+        cache = Cache([[KVRequest(kv_heads, hd, None, bf, hd, None, keep)], [KVRequest(kv_heads, hd, None, bf)],
+                       [StateRequest((gh, hd, hd), torch.float32)]], batch * (context + 64), batch, dev)
+        slots = [cache.begin() for _ in range(batch)]
+        for sl in slots:
+            cache.reserve(sl, context)
+            cache.length[sl] = context
+        ctx = build_context(cache, [(sl, [0], []) for sl in slots], dev)
+        for e in (0, 1):
+            v = cache.views(e)[0]
+            v.k.normal_(), v.v.normal_()
+        m, f, stt = cache.views(0)[0], cache.views(1)[0], cache.views(2)[0].state
+        q = torch.randn(batch, heads * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        table = ctx.tables[m.group]
+        keys = min(window, context + 1) + keep
+        ns = api.masked_decode_splits(batch, kv_heads, heads // kv_heads, table.shape[1], window, None)
+        ws = api.attention_decode_ws(batch, heads, hd, ns, dev)
+        us = timed(lambda: api.attention_decode_masked_bf16(q, o, None, 1.0, m.k, m.v, ctx.row_pos, table, heads, kv_heads, hd, window, None,
+                                                            hd ** -0.5, ns, ws[0], ws[1], None, None, sink, cap, keep))
+        out[f"window_attention_decode_b{batch}"] = dict(bytes_rec(us, batch * kv_heads * keys * 2 * hd * 2), keys=keys)
+        nsplit = api.decode_splits(batch, kv_heads, heads // kv_heads, ctx.tables[f.group].shape[1])
+        ws2 = api.attention_decode_ws(batch, heads, hd, nsplit, dev)
+        us = timed(lambda: api.attention_decode_bf16(q, o, f.k, f.v, ctx.row_pos, ctx.tables[f.group], heads, kv_heads, hd, None,
+                                                     hd ** -0.5, nsplit, *ws2))
+        out[f"qwen3_attention_decode_b{batch}"] = dict(bytes_rec(us, batch * kv_heads * (context + 1) * 2 * hd * 2), keys=context + 1)
+        x = torch.randn(batch, 3 * gh * hd, device=dev).to(bf)
+        z = torch.randn(batch, gh * hd, device=dev)
+        zb = torch.zeros(gh * hd, device=dev)
+        lo = torch.empty(batch, gh * hd, dtype=torch.float32, device=dev)
+        us = timed(lambda: api.gated_linear_attention(x[:, :gh * hd], x[:, gh * hd:2 * gh * hd], x[:, 2 * gh * hd:], lo, stt, None,
+                                                           ctx.row_pos, ctx.seq_slot, z, zb, 16.0, hd ** -0.5, batch, gh, hd, hd))
+        out[f"gated_linear_attention_decode_b{batch}"] = bytes_rec(us, batch * gh * hd * hd * 4 * 2)
+        a = torch.randn(batch, width, device=dev).to(bf)
+        us = timed(lambda: moe.forward(Ctx(), a))
+        experts_read = min(32, batch * 4) + 1              # at most: every pair another expert, and the shared one
+        out[f"routed_feed_forward_decode_b{batch}"] = bytes_rec(us, experts_read * 3 * eff * width * 2)
+        us = timed(lambda: dense.forward(None, a))
+        out[f"qwen3_feed_forward_decode_b{batch}"] = bytes_rec(us, 3 * ff_qwen * width * 2)
+        del cache, q, o, x, z, lo, a
+    torch.cuda.empty_cache()
+    return out
+
+
+PIBULIX_WINDOW = 1024
+
+
 def run_design(args):
-    """``--design nilivik``: prefill and decode of the Nilivik decoder at Qwen3 layer sizes (random weights,
+    """``--design nilivik`` / ``--design pibulix``: prefill and decode of that decoder at Qwen3 layer sizes (random weights,
     ``--layers`` layers, default 4) beside Qwen3 itself at the same width, layer count and parameters a
     layer, and the design's mixer kernels alone beside Qwen3's attention kernels. One JSON line."""
     import torch
@@ -513,10 +669,15 @@ def run_design(args):
            "data": "synthetic: random weights, uniform random token ids", "peaks": pk, "sizes": {}}
     for size in args.design_sizes.split(","):
         q = dict(SIZES[size]["config"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True)
-        n = nilivik_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers,
-                           vocab, chunk)
-        rec = {"width": q["hidden_size"], "nilivik_ff": n["layers"][0]["mlp"]["ff"]}
-        for name, cfg_d in (("nilivik", n), ("qwen3", q)):
+        if args.design == "pibulix":
+            n = pibulix_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers,
+                               vocab, PIBULIX_WINDOW)
+            rec = {"width": q["hidden_size"], "window": PIBULIX_WINDOW, "expert_ff": n["layers"][1]["mlp"]["expert"]["ff"]}
+        else:
+            n = nilivik_config(q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"], q["intermediate_size"], layers,
+                               vocab, chunk)
+            rec = {"width": q["hidden_size"], "nilivik_ff": n["layers"][0]["mlp"]["ff"]}
+        for name, cfg_d in ((args.design, n), ("qwen3", q)):
             model = dk.random_model(dk.config_from_dict(cfg_d), seed=0, dtype=torch.bfloat16)
             r = {"weight_mb_per_step": round(model.weight_bytes_per_step() / 1e6, 1), "prefill": {}, "decode": {}}
             for tokens in (2048, 8192):
@@ -530,8 +691,12 @@ def run_design(args):
             rec[name] = r
             del model
             torch.cuda.empty_cache()
-        rec["kernels"] = kernel_times(torch, dk, pk, q["num_attention_heads"], q["num_key_value_heads"],
-                                      q["num_attention_heads"] // 2, chunk)
+        if args.design == "pibulix":
+            rec["kernels"] = pibulix_kernel_times(torch, dk, pk, q["hidden_size"], q["num_attention_heads"], q["num_key_value_heads"],
+                                                  q["intermediate_size"], PIBULIX_WINDOW)
+        else:
+            rec["kernels"] = kernel_times(torch, dk, pk, q["num_attention_heads"], q["num_key_value_heads"],
+                                          q["num_attention_heads"] // 2, chunk)
         out["sizes"][size] = rec
     api.gemm_tc_check()
     print(json.dumps(out))
@@ -737,7 +902,7 @@ def main():
     ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --prefill-only: a prompt of another length")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
-    ap.add_argument("--design", default=None, choices=["nilivik"],
+    ap.add_argument("--design", default=None, choices=["nilivik", "pibulix"],
                     help="instead of the default workload: prefill and decode of this design at Qwen3 layer sizes beside Qwen3 "
                          "itself at equal size, and its mixer kernels alone (one JSON line of its own)")
     ap.add_argument("--design-sizes", default="4b,8b", help="with --design: which of the layer sizes")

@@ -1109,8 +1109,8 @@ MOE_TILE_ROWS = 64
 
 def moe_tiles_take(x, expert_ff):
     """Whether a step's routed experts run as tiles on the tensor cores: bfloat16, more than 32 tokens, inner
-    sizes (width and expert size) that are multiples of 32."""
-    return x.dtype == torch.bfloat16 and x.shape[0] > 32 and x.shape[1] % 32 == 0 and expert_ff % 32 == 0
+    sizes (width and expert size) that are multiples of 64."""
+    return x.dtype == torch.bfloat16 and x.shape[0] > 32 and x.shape[1] % 64 == 0 and expert_ff % 64 == 0
 
 
 def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, act=0, scratch=None):
@@ -1124,8 +1124,8 @@ def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, a
     top = idx.shape[1]
     E, ff = w_down.shape[0], w_down.shape[2]
     if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape[1] != W or idx.shape[0] != T or wt.shape != idx.shape or \
-            out.shape != (T, W) or W % 32 or ff % 32 or E > MOE_MAX_EXPERTS or (shared is not None and shared.shape != (T, W)):
-        raise KernelError("moe_experts_tiles: shapes do not match (inner sizes in steps of 32)")
+            out.shape != (T, W) or W % 64 or ff % 64 or E > MOE_MAX_EXPERTS or (shared is not None and shared.shape != (T, W)):
+        raise KernelError("moe_experts_tiles: shapes do not match (inner sizes in steps of 64)")
     P = T * top
     max_tiles = (P + MOE_TILE_ROWS - 1) // MOE_TILE_ROWS + E
     dev = x.device
@@ -1141,3 +1141,33 @@ def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, a
            "moe_up_tiles")
     _check(lib, lib.dk_moe_down_tiles(_p(mid), _p(w_down), _p(tiles), max_tiles, _p(y), W, ff, _stream()), "moe_down_tiles")
     _check(lib, lib.dk_moe_sum(_p(y), _p(inv), _p(wt), _p(shared), _p(shared_gate), _p(out), T, W, top, _stream()), "moe_sum")
+
+
+def gated_linear_attention_takes_warps(head_dim, v_head_dim):
+    """Head sizes of the warp form of gated linear attention: keys of 32, 64, 128 or 256, values in steps of 8."""
+    return head_dim in (32, 64, 128, 256) and v_head_dim % 8 == 0 and v_head_dim <= 256
+
+
+def gated_linear_attention(q, k, v, out, state, cu_q, seq_pos0, seq_slot, z, z_bias, tau, q_scale, n_seq, n_heads, head_dim,
+                           v_head_dim):
+    """``gated_linear_attention_step`` by the kernel that suits the head sizes: a warp per 8 value columns with
+    the state in registers (after a kernel that turns ``z`` into the decays, in place) where
+    ``gated_linear_attention_takes_warps``, else the block form. Either runs the recurrence token by token in
+    float32, for prompts, portions and single tokens alike."""
+    if not gated_linear_attention_takes_warps(head_dim, v_head_dim):
+        return gated_linear_attention_step(q, k, v, out, state, cu_q, seq_pos0, seq_slot, z, z_bias, tau, q_scale, n_seq, n_heads,
+                                           head_dim, v_head_dim)
+    _need_rows(q, "q"), _need_rows(k, "k", q.dtype), _need_rows(v, "v", q.dtype)
+    _need(out, "out", torch.float32, 2), _need(state, "state", torch.float32, 4)
+    _need(z, "z", torch.float32, 2), _need(z_bias, "z_bias", torch.float32, 1)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1), _need(seq_slot, "seq_slot", torch.int32, 1)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.shape[1] != n_heads * head_dim or \
+            v.shape[1] != n_heads * v_head_dim or tuple(state.shape[1:]) != (n_heads, head_dim, v_head_dim) or \
+            z.shape != (q.shape[0], n_heads * head_dim) or z_bias.numel() != n_heads * head_dim or not tau > 0 or \
+            out.shape != (q.shape[0], n_heads * v_head_dim):
+        raise KernelError("gated_linear_attention: shapes do not match")
+    lib = _lib("linear_attention.cu")
+    _check(lib, lib.dk_gated_linear_attention_warp(_dt(q), _p(q), _p(k), _p(v), c_longlong(q.stride(0)), _p(z), _p(z_bias),
+                                                   c_float(1.0 / tau), c_longlong(q.shape[0]), _p(out), _p(state), _p(cu_q),
+                                                   _p(seq_pos0), _p(seq_slot), c_float(q_scale), n_seq, n_heads, head_dim,
+                                                   v_head_dim, _stream()), "gated_linear_attention", 2)

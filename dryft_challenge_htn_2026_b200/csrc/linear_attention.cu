@@ -107,6 +107,289 @@ linear_attention_step_kernel(const T* q, const T* k, const T* v, long long ld, f
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gated linear attention, a warp per (sequence, head, 8 value columns): lane l keeps the state rows of key channels
+// DPL * l .. DPL * l + DPL - 1 (DPL = hd / 32) for its 8 columns in registers, DPL * 8 numbers. A token costs the
+// warp DPL * 16 multiply-adds and 9 shuffles (the 8 column sums over the lanes are folded by halves: 4, 2, 1
+// exchanges, then two more on the one value left), no shared memory and no barrier; the state's own chain is one
+// multiply-add a token, the loads of later tokens do not wait for it. The decays come as float32 rows
+// (gla_decay_kernel makes them from the projection's rows, once for all column groups).
+template <int N> __device__ __forceinline__ void ld_vec(const float* p, float (&f)[N], bool vec) {
+    if (vec && N == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+    } else if (vec && N == 8) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; i++) f[i] = p[i];
+    }
+}
+template <int N> __device__ __forceinline__ void ld_vec(const bf16* p, float (&f)[N], bool vec) {
+    if (vec && N == 8) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 x = __bfloat1622float2(h[i]);
+            f[2 * i] = x.x, f[2 * i + 1] = x.y;
+        }
+    } else if (vec && N == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const float2 x = __bfloat1622float2(h[i]);
+            f[2 * i] = x.x, f[2 * i + 1] = x.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; i++) f[i] = __bfloat162float(p[i]);
+    }
+}
+
+// alpha = sigmoid(z + b)^(1/tau) = exp(log sigmoid(z + b) / tau), in place over the float32 rows z [rows, n]
+__global__ void gla_decay_kernel(float* z, const float* __restrict__ bias, float inv_tau, size_t total, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float x = z[i] + bias[i % n];
+    z[i] = expf((fminf(x, 0.f) - log1pf(expf(-fabsf(x)))) * inv_tau);
+}
+
+template <typename T, int DPL>
+__global__ void __launch_bounds__(128)
+gla_warp_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
+                const float* __restrict__ alpha, float* __restrict__ out, float* state, const int* cu_q, const int* seq_pos0,
+                const int* seq_slot, int nh, int hdv, float q_scale, int vec) {
+    constexpr int HDK = 32 * DPL;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int c0 = (blockIdx.z * 4 + warp) * 8;
+    if (c0 >= hdv) return;
+    const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
+    const size_t ow = (size_t)nh * hdv;
+    // after the folds lane l holds the sum of column 4 * bit4 + 2 * bit3 + bit2 of its number
+    const int my_col = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if (seq_pos0[s] < 0) {        // a padding row: zeros out, state untouched
+        if ((lane & 3) == 0)
+            for (int t = r0; t < r1; t++) out[(size_t)t * ow + (size_t)h * hdv + c0 + my_col] = 0.f;
+        return;
+    }
+    float* S = state + ((size_t)seq_slot[s] * nh + h) * (size_t)HDK * hdv + (size_t)(DPL * lane) * hdv + c0;
+    float st[DPL][8];
+#pragma unroll
+    for (int i = 0; i < DPL; i++) ld_vec<8>(S + (size_t)i * hdv, st[i], true);
+    const size_t qk_at = (size_t)h * HDK + DPL * lane, v_at = (size_t)h * hdv + c0;
+    const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+#pragma unroll 2
+    for (int t = r0; t < r1; t++) {
+        float qv[DPL], kv[DPL], av[DPL], vv[8];
+        ld_vec<DPL>(q + (size_t)t * ld + qk_at, qv, vec);
+        ld_vec<DPL>(k + (size_t)t * ld + qk_at, kv, vec);
+        ld_vec<DPL>(alpha + (size_t)t * nh * HDK + qk_at, av, vec);
+        ld_vec<8>(v + (size_t)t * ld + v_at, vv, vec);
+        float o[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) o[c] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) {
+            const float qs = qv[i] * q_scale;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                st[i][c] = fmaf(av[i], st[i][c], kv[i] * vv[c]);
+                o[c] = fmaf(st[i][c], qs, o[c]);
+            }
+        }
+        float r4[4], r2[2], r;
+#pragma unroll
+        for (int c = 0; c < 4; c++) r4[c] = (hi16 ? o[4 + c] : o[c]) + __shfl_xor_sync(0xffffffffu, hi16 ? o[c] : o[4 + c], 16);
+#pragma unroll
+        for (int c = 0; c < 2; c++) r2[c] = (hi8 ? r4[2 + c] : r4[c]) + __shfl_xor_sync(0xffffffffu, hi8 ? r4[c] : r4[2 + c], 8);
+        r = (hi4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? r2[0] : r2[1], 4);
+        r += __shfl_xor_sync(0xffffffffu, r, 2);
+        r += __shfl_xor_sync(0xffffffffu, r, 1);
+        if ((lane & 3) == 0) out[(size_t)t * ow + v_at + my_col] = r;
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; i++) {
+        *reinterpret_cast<float4*>(S + (size_t)i * hdv) = make_float4(st[i][0], st[i][1], st[i][2], st[i][3]);
+        *reinterpret_cast<float4*>(S + (size_t)i * hdv + 4) = make_float4(st[i][4], st[i][5], st[i][6], st[i][7]);
+    }
+}
+
+// The same with the rows staged: the block's four warps share a head, so its q, k and decay rows (and the block's 32
+// value columns) of 16 tokens at a time come into shared memory by cp.async, two stages in turn, and the warps read
+// them from there: the loads of the next 16 tokens run under the arithmetic of these. Rows on 16-byte boundaries.
+#define GLA_NT 16
+__device__ __forceinline__ void gla_cp16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+template <typename T, int DPL>
+__global__ void __launch_bounds__(128)
+gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
+                       const float* __restrict__ alpha, float* __restrict__ out, float* state, const int* cu_q,
+                       const int* seq_pos0, const int* seq_slot, int nh, int hdv, float q_scale) {
+    constexpr int HDK = 32 * DPL;
+    constexpr int QB = GLA_NT * HDK * (int)sizeof(T), AB = GLA_NT * HDK * 4, VB = GLA_NT * 32 * (int)sizeof(T);
+    constexpr int STAGE = 2 * QB + AB + VB;
+    extern __shared__ __align__(16) unsigned char gla_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int col0 = blockIdx.z * 32, c0 = col0 + warp * 8;
+    const bool active = c0 < hdv;
+    const int cols_here = min(32, hdv - col0);
+    const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
+    const size_t ow = (size_t)nh * hdv;
+    const int my_col = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if (seq_pos0[s] < 0) {
+        if (active && (lane & 3) == 0)
+            for (int t = r0; t < r1; t++) out[(size_t)t * ow + (size_t)h * hdv + c0 + my_col] = 0.f;
+        return;
+    }
+    float* S = state + ((size_t)seq_slot[s] * nh + h) * (size_t)HDK * hdv + (size_t)(DPL * lane) * hdv + c0;
+    float st[DPL][8];
+#pragma unroll
+    for (int i = 0; i < DPL; i++) {
+        if (active) ld_vec<8>(S + (size_t)i * hdv, st[i], true);
+        else
+#pragma unroll
+            for (int c = 0; c < 8; c++) st[i][c] = 0.f;
+    }
+    const int n_chunks = (r1 - r0 + GLA_NT - 1) / GLA_NT;
+    constexpr int QP = HDK * (int)sizeof(T) / 16, AP = HDK * 4 / 16;         // 16-byte pieces a token
+    const int VP = cols_here * (int)sizeof(T) / 16;
+    auto issue = [&](int c) {
+        if (c < n_chunks) {
+            unsigned char* base = gla_smem + (c & 1) * STAGE;
+            const int t0 = r0 + c * GLA_NT, nt = min(GLA_NT, r1 - t0);
+            for (int i = tid; i < nt * QP; i += 128) {
+                const int tt = i / QP, pc = i % QP;
+                const size_t src = ((size_t)(t0 + tt) * ld + (size_t)h * HDK) * sizeof(T) + pc * 16;
+                gla_cp16(base + tt * (HDK * sizeof(T)) + pc * 16, reinterpret_cast<const unsigned char*>(q) + src);
+                gla_cp16(base + QB + tt * (HDK * sizeof(T)) + pc * 16, reinterpret_cast<const unsigned char*>(k) + src);
+            }
+            for (int i = tid; i < nt * AP; i += 128) {
+                const int tt = i / AP, pc = i % AP;
+                gla_cp16(base + 2 * QB + tt * (HDK * 4) + pc * 16,
+                         reinterpret_cast<const unsigned char*>(alpha + (size_t)(t0 + tt) * nh * HDK + (size_t)h * HDK) + pc * 16);
+            }
+            for (int i = tid; i < nt * VP; i += 128) {
+                const int tt = i / VP, pc = i % VP;
+                gla_cp16(base + 2 * QB + AB + tt * (32 * sizeof(T)) + pc * 16,
+                         reinterpret_cast<const unsigned char*>(v + (size_t)(t0 + tt) * ld + (size_t)h * hdv + col0) + pc * 16);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
+    issue(0);
+    for (int c = 0; c < n_chunks; c++) {
+        issue(c + 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const unsigned char* base = gla_smem + (c & 1) * STAGE;
+        const T* sq = reinterpret_cast<const T*>(base);
+        const T* sk = reinterpret_cast<const T*>(base + QB);
+        const float* sa = reinterpret_cast<const float*>(base + 2 * QB);
+        const T* sv = reinterpret_cast<const T*>(base + 2 * QB + AB);
+        const int t0 = r0 + c * GLA_NT, nt = min(GLA_NT, r1 - t0);
+        if (active) {
+#pragma unroll 4
+            for (int tt = 0; tt < nt; tt++) {     // unrolled: one token's folds run under the next tokens' multiply-adds
+                float qv[DPL], kv[DPL], av[DPL], vv[8];
+                ld_vec<DPL>(sq + tt * HDK + DPL * lane, qv, true);
+                ld_vec<DPL>(sk + tt * HDK + DPL * lane, kv, true);
+                ld_vec<DPL>(sa + tt * HDK + DPL * lane, av, true);
+                ld_vec<8>(sv + tt * 32 + warp * 8, vv, true);
+                float o[8];
+#pragma unroll
+                for (int cc = 0; cc < 8; cc++) o[cc] = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) {
+                    const float qs = qv[i] * q_scale;
+#pragma unroll
+                    for (int cc = 0; cc < 8; cc++) {
+                        st[i][cc] = fmaf(av[i], st[i][cc], kv[i] * vv[cc]);
+                        o[cc] = fmaf(st[i][cc], qs, o[cc]);
+                    }
+                }
+                float r4[4], r2[2], r;
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++)
+                    r4[cc] = (hi16 ? o[4 + cc] : o[cc]) + __shfl_xor_sync(0xffffffffu, hi16 ? o[cc] : o[4 + cc], 16);
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++)
+                    r2[cc] = (hi8 ? r4[2 + cc] : r4[cc]) + __shfl_xor_sync(0xffffffffu, hi8 ? r4[cc] : r4[2 + cc], 8);
+                r = (hi4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? r2[0] : r2[1], 4);
+                r += __shfl_xor_sync(0xffffffffu, r, 2);
+                r += __shfl_xor_sync(0xffffffffu, r, 1);
+                if ((lane & 3) == 0) out[(size_t)(t0 + tt) * ow + (size_t)h * hdv + c0 + my_col] = r;
+            }
+        }
+        __syncthreads();              // the stage is free for the chunk after next
+    }
+    if (active) {
+#pragma unroll
+        for (int i = 0; i < DPL; i++) {
+            *reinterpret_cast<float4*>(S + (size_t)i * hdv) = make_float4(st[i][0], st[i][1], st[i][2], st[i][3]);
+            *reinterpret_cast<float4*>(S + (size_t)i * hdv + 4) = make_float4(st[i][4], st[i][5], st[i][6], st[i][7]);
+        }
+    }
+}
+
+template <typename T>
+static int launch_gla_warp(const void* q, const void* k, const void* v, long long ld, const float* alpha, float* out,
+                           float* state, const int* cu_q, const int* seq_pos0, const int* seq_slot, int n_seq, int nh, int hd,
+                           int hdv, float q_scale, int vec, long long n_tok_max, cudaStream_t st) {
+    const dim3 grid(n_seq, nh, (hdv + 31) / 32), block(128);
+#define GLA_WARP(D)                                                                                                    \
+    if (hd == 32 * D)                                                                                                  \
+        return dk_launch(gla_warp_kernel<T, D>, grid, block, 0, st, (const T*)q, (const T*)k, (const T*)v, ld, alpha, out, \
+                         state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale, vec);
+    if (vec && n_tok_max > 4) {      // portions: staged rows (single tokens have nothing to run ahead of)
+#define GLA_STAGED(D)                                                                                                      \
+    if (hd == 32 * D) {                                                                                                    \
+        const size_t smem = 2 * (size_t)(2 * GLA_NT * 32 * D * sizeof(T) + GLA_NT * 32 * D * 4 + GLA_NT * 32 * sizeof(T));  \
+        if (smem > 48 * 1024)                                                                                              \
+            cudaFuncSetAttribute(gla_warp_staged_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        return dk_launch(gla_warp_staged_kernel<T, D>, grid, block, smem, st, (const T*)q, (const T*)k, (const T*)v, ld,   \
+                         alpha, out, state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale);                                   \
+    }
+        GLA_STAGED(1) GLA_STAGED(2) GLA_STAGED(4) GLA_STAGED(8)
+#undef GLA_STAGED
+    }
+    GLA_WARP(1) GLA_WARP(2) GLA_WARP(4) GLA_WARP(8)
+#undef GLA_WARP
+    return (int)cudaErrorInvalidValue;
+}
+
+// z [rows, nh * hd] float32 is overwritten by the decays. Head sizes: hd 32, 64, 128 or 256, hdv a multiple of 8.
+DK_EXPORT int dk_gated_linear_attention_warp(int dtype, const void* q, const void* k, const void* v, long long ld, float* z,
+                                             const float* zbias, float inv_tau, long long n_rows, float* out, float* state,
+                                             const int* cu_q, const int* seq_pos0, const int* seq_slot, float q_scale, int n_seq,
+                                             int nh, int hd, int hdv, cudaStream_t st) {
+    const long long n_tok_max = cu_q ? n_rows : 1;      // the most tokens a sequence can bring: all rows, or one without cu_q
+    if (hdv % 8 || hdv > 256 || (hd != 32 && hd != 64 && hd != 128 && hd != 256)) return (int)cudaErrorInvalidValue;
+    const size_t total = (size_t)n_rows * nh * hd;
+    int e = dk_launch(gla_decay_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, z, zbias, inv_tau, total, nh * hd);
+    if (e) return e;
+    // whole 16-byte pieces: rows of q, k, v that start on 16-byte boundaries
+    const int esz = dtype == 0 ? 4 : 2;
+    const int vec = ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 16 == 0 && (ld * esz) % 16 == 0 && (hd * esz) % 16 == 0 &&
+                    (hdv * esz) % 16 == 0;
+    if (dtype == 0)
+        return launch_gla_warp<float>(q, k, v, ld, z, out, state, cu_q, seq_pos0, seq_slot, n_seq, nh, hd, hdv, q_scale, vec, n_tok_max, st);
+    return launch_gla_warp<bf16>(q, k, v, ld, z, out, state, cu_q, seq_pos0, seq_slot, n_seq, nh, hd, hdv, q_scale, vec, n_tok_max, st);
+}
+
 // out[t] = rmsnorm(o[t]) * w * sigmoid(gate[t]) * out_scale, the norm over each group of ``group`` columns of
 // the row (the whole row of all heads, width n, or one head at a time with a weight of the head's size,
 // shared by the heads); gate_act 1: SiLU of the gate instead of its sigmoid. Block (token, group).

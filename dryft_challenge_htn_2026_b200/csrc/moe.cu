@@ -14,7 +14,8 @@
 #include "common.cuh"
 
 #define MOE_MAX_EXPERTS 256
-#define ROUTE_WARPS 4
+#define ROUTE_WARPS 8
+#define ROUTE_TOKENS 8
 
 // (value, index) with the larger value, the lower index among equal values, over the warp
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -26,39 +27,71 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
+// A block routes up to ROUTE_TOKENS tokens: their rows sit in shared memory, each of the 8 warps takes every 8th
+// expert and works out its logit for all the block's tokens at once (the router's row is read once a block, 16 bytes
+// a lane where the width allows), then warp t makes the choice for token t.
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_route_kernel(const T* x, int W, const float* __restrict__ wr, const float* __restrict__ corr,
                  const float* __restrict__ wsg, int E, int top, int groups, int keep, float scale, int* idx, float* wt,
-                 float* sgate, int n_tok) {
-    __shared__ float s_all[ROUTE_WARPS][MOE_MAX_EXPERTS];
-    __shared__ float c_all[ROUTE_WARPS][MOE_MAX_EXPERTS];
-    __shared__ float g_all[ROUTE_WARPS][MOE_MAX_EXPERTS];
+                 float* sgate, int n_tok, int tokens_per_block) {
+    extern __shared__ __align__(16) unsigned char route_smem[];
+    float* s_all = reinterpret_cast<float*>(route_smem);                 // [tokens][E] sigmoid scores
+    float* c_all = s_all + tokens_per_block * E;                         // [tokens][E] choice scores
+    float* g_all = c_all + tokens_per_block * E;                         // [tokens][E] group scores
+    T* xs = reinterpret_cast<T*>(g_all + tokens_per_block * E);          // [tokens][W]
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int t = blockIdx.x * ROUTE_WARPS + w;
-    if (t >= n_tok) return;
-    float* s = s_all[w];
-    float* c = c_all[w];
-    float* gs = g_all[w];
-    const T* xr = x + (size_t)t * W;
-    for (int e = 0; e < E; e++) {
-        float acc = 0.f;
-        for (int k = lane; k < W; k += 32) acc = fmaf(wr[(size_t)e * W + k], to_f(xr[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            s[e] = 1.f / (1.f + expf(-acc));
-            c[e] = s[e] + (corr ? corr[e] : 0.f);
+    const int t0 = blockIdx.x * tokens_per_block;
+    const int nt = min(tokens_per_block, n_tok - t0);
+    for (int i = threadIdx.x; i < nt * W; i += blockDim.x) xs[i] = x[(size_t)t0 * W + i];
+    __syncthreads();
+    const bool vec = W % 4 == 0;
+    for (int e = w; e <= E; e += ROUTE_WARPS) {         // e == E: the shared expert's gate
+        const float* row = e < E ? wr + (size_t)e * W : wsg;
+        if (row == nullptr) continue;
+        float acc[ROUTE_TOKENS];
+#pragma unroll
+        for (int tt = 0; tt < ROUTE_TOKENS; tt++) acc[tt] = 0.f;
+        if (vec) {
+#pragma unroll 2
+            for (int k = lane * 4; k < W; k += 128) {
+                const float4 r = __ldg(reinterpret_cast<const float4*>(row + k));
+#pragma unroll
+                for (int tt = 0; tt < ROUTE_TOKENS; tt++)
+                    if (tt < nt) {
+                        const T* xr = xs + tt * W + k;
+                        acc[tt] = fmaf(r.x, to_f(xr[0]), fmaf(r.y, to_f(xr[1]), fmaf(r.z, to_f(xr[2]), fmaf(r.w, to_f(xr[3]), acc[tt]))));
+                    }
+            }
+        } else {
+            for (int k = lane; k < W; k += 32)
+#pragma unroll
+                for (int tt = 0; tt < ROUTE_TOKENS; tt++)
+                    if (tt < nt) acc[tt] = fmaf(row[k], to_f(xs[tt * W + k]), acc[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < ROUTE_TOKENS; tt++) {
+            if (tt >= nt) continue;
+            const float z = warp_sum(acc[tt]);
+            if (lane == 0) {
+                const float sg = 1.f / (1.f + expf(-z));
+                if (e < E) {
+                    s_all[tt * E + e] = sg;
+                    c_all[tt * E + e] = sg + (corr ? corr[e] : 0.f);
+                } else {
+                    sgate[t0 + tt] = sg;
+                }
+            }
         }
     }
-    if (wsg != nullptr) {
-        float acc = 0.f;
-        for (int k = lane; k < W; k += 32) acc = fmaf(wsg[k], to_f(xr[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) sgate[t] = 1.f / (1.f + expf(-acc));
-    }
-    __syncwarp();
+    __syncthreads();
+    if (w >= nt) return;
+    const int t = t0 + w;
+    float* s = s_all + w * E;
+    float* c = c_all + w * E;
+    float* gs = g_all + w * E;
     if (groups > 1 && keep < groups) {
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {       // a group's score: its two largest choice scores
@@ -110,8 +143,32 @@ __device__ __forceinline__ float moe_act(float z, int act) {
     return z / (1.f + expf(-z));
 }
 
-// Block (pair, slice of ff): mid[pair][f] = act(W_gu[e][f] . x) * (W_gu[e][ff + f] . x), W_gu [E, 2 ff, W].
-template <typename T>
+// 16 bytes of a row as floats: 8 bfloat16 or 4 float32 values
+template <typename T> struct Vec;
+template <> struct Vec<bf16> {
+    static constexpr int N = 8;
+    __device__ static __forceinline__ void load(const bf16* p, float (&f)[8]) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float2 x = __bfloat1622float2(h[i]);
+            f[2 * i] = x.x, f[2 * i + 1] = x.y;
+        }
+    }
+};
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    __device__ static __forceinline__ void load(const float* p, float (&f)[4]) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+        f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+    }
+};
+
+// Block (pair, slice of ff): mid[pair][f] = act(W_gu[e][f] . x) * (W_gu[e][ff + f] . x), W_gu [E, 2 ff, W]. A warp an
+// output: its gate row and its up row streamed 16 bytes a lane at a time (VEC; rows then start on 16-byte
+// boundaries), several requests in flight, or element by element for other widths.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(128)
 moe_up_rows_kernel(const T* x, int W, const T* __restrict__ wgu, const int* idx, T* mid, int ff, int top, int rows_per_block,
                    int act) {
@@ -125,13 +182,30 @@ moe_up_rows_kernel(const T* x, int W, const T* __restrict__ wgu, const int* idx,
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int f_end = min(ff, (int)(blockIdx.y + 1) * rows_per_block);
     const T* base = wgu + (size_t)e * 2 * ff * W;
+    constexpr int N = Vec<T>::N;
     for (int f = blockIdx.y * rows_per_block + w; f < f_end; f += 4) {
         const T* g = base + (size_t)f * W;
         const T* u = base + (size_t)(ff + f) * W;
         float ag = 0.f, au = 0.f;
-        for (int k = lane; k < W; k += 32) {
-            ag = fmaf(to_f(g[k]), xs[k], ag);
-            au = fmaf(to_f(u[k]), xs[k], au);
+        if (VEC) {
+#pragma unroll 4
+            for (int k = lane * N; k < W; k += 32 * N) {
+                float gv[N], uv[N], xv[N];
+                Vec<T>::load(g + k, gv);
+                Vec<T>::load(u + k, uv);
+#pragma unroll
+                for (int i = 0; i < N; i += 4) *reinterpret_cast<float4*>(xv + i) = *reinterpret_cast<const float4*>(xs + k + i);
+#pragma unroll
+                for (int i = 0; i < N; i++) {
+                    ag = fmaf(gv[i], xv[i], ag);
+                    au = fmaf(uv[i], xv[i], au);
+                }
+            }
+        } else {
+            for (int k = lane; k < W; k += 32) {
+                ag = fmaf(to_f(g[k]), xs[k], ag);
+                au = fmaf(to_f(u[k]), xs[k], au);
+            }
         }
         ag = warp_sum(ag);
         au = warp_sum(au);
@@ -140,7 +214,7 @@ moe_up_rows_kernel(const T* x, int W, const T* __restrict__ wgu, const int* idx,
 }
 
 // Block (token, slice of the width): out[t][c] = sum_j wt[t][j] (W_d[e_j][c] . mid[t*top + j]) + sgate[t] * shared[t][c].
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(128)
 moe_down_rows_kernel(const T* mid, const T* __restrict__ wd, const int* idx, const float* wt, const T* shared,
                      const float* sgate, T* out, int W, int ff, int top, int rows_per_block) {
@@ -153,12 +227,25 @@ moe_down_rows_kernel(const T* mid, const T* __restrict__ wd, const int* idx, con
     __syncthreads();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int c_end = min(W, (int)(blockIdx.y + 1) * rows_per_block);
+    constexpr int N = Vec<T>::N;
     for (int c = blockIdx.y * rows_per_block + w; c < c_end; c += 4) {
         float acc = 0.f;
         for (int j = 0; j < top; j++) {
             const T* row = wd + ((size_t)idx[(size_t)t * top + j] * W + c) * ff;
             float a = 0.f;
-            for (int k = lane; k < ff; k += 32) a = fmaf(to_f(row[k]), ms[j * ff + k], a);
+            if (VEC) {
+#pragma unroll 4
+                for (int k = lane * N; k < ff; k += 32 * N) {
+                    float rv[N], mv[N];
+                    Vec<T>::load(row + k, rv);
+#pragma unroll
+                    for (int i = 0; i < N; i += 4) *reinterpret_cast<float4*>(mv + i) = *reinterpret_cast<const float4*>(ms + j * ff + k + i);
+#pragma unroll
+                    for (int i = 0; i < N; i++) a = fmaf(rv[i], mv[i], a);
+                }
+            } else {
+                for (int k = lane; k < ff; k += 32) a = fmaf(to_f(row[k]), ms[j * ff + k], a);
+            }
             acc += a;
         }
         acc = warp_sum(acc);
@@ -169,48 +256,68 @@ moe_down_rows_kernel(const T* mid, const T* __restrict__ wd, const int* idx, con
     }
 }
 
+template <typename T>
+static int launch_route(const void* x, int W, const float* wr, const float* corr, const float* wsg, int E, int top, int groups,
+                        int keep, float scale, int* idx, float* wt, float* sgate, int n_tok, cudaStream_t st) {
+    int tpb = ROUTE_TOKENS;
+    auto need = [&](int t) { return sizeof(float) * 3 * (size_t)t * E + sizeof(T) * (size_t)t * W; };
+    while (tpb > 1 && need(tpb) > 160 * 1024) tpb >>= 1;
+    const size_t smem = need(tpb);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return dk_launch(moe_route_kernel<T>, dim3((n_tok + tpb - 1) / tpb), dim3(32 * ROUTE_WARPS), smem, st, (const T*)x, W, wr, corr,
+                     wsg, E, top, groups, keep, scale, idx, wt, sgate, n_tok, tpb);
+}
+
 DK_EXPORT int dk_moe_route(int dtype, const void* x, int W, const float* wr, const float* corr, const float* wsg, int E,
                            int top, int groups, int keep, float scale, int* idx, float* wt, float* sgate, int n_tok,
                            cudaStream_t st) {
     if (E < 1 || E > MOE_MAX_EXPERTS || top < 1 || top > 32 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups)
         return (int)cudaErrorInvalidValue;
-    const dim3 grid((n_tok + ROUTE_WARPS - 1) / ROUTE_WARPS), block(32 * ROUTE_WARPS);
-    if (dtype == 0)
-        return dk_launch(moe_route_kernel<float>, grid, block, 0, st, (const float*)x, W, wr, corr, wsg, E, top, groups,
-                         keep, scale, idx, wt, sgate, n_tok);
-    return dk_launch(moe_route_kernel<bf16>, grid, block, 0, st, (const bf16*)x, W, wr, corr, wsg, E, top, groups, keep,
-                     scale, idx, wt, sgate, n_tok);
+    if (dtype == 0) return launch_route<float>(x, W, wr, corr, wsg, E, top, groups, keep, scale, idx, wt, sgate, n_tok, st);
+    return launch_route<bf16>(x, W, wr, corr, wsg, E, top, groups, keep, scale, idx, wt, sgate, n_tok, st);
+}
+
+template <typename T, bool VEC>
+static int launch_up(const void* x, int W, const void* wgu, const int* idx, void* mid, int ff, int top, int n_tok, int act,
+                     cudaStream_t st) {
+    const int rpb = 16;
+    const dim3 grid(n_tok * top, (ff + rpb - 1) / rpb), block(128);
+    const size_t smem = sizeof(float) * (size_t)W;
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_rows_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return dk_launch(moe_up_rows_kernel<T, VEC>, grid, block, smem, st, (const T*)x, W, (const T*)wgu, idx, (T*)mid, ff, top, rpb, act);
+}
+
+template <typename T, bool VEC>
+static int launch_down(const void* mid, const void* wd, const int* idx, const float* wt, const void* shared, const float* sgate,
+                       void* out, int W, int ff, int top, int n_tok, cudaStream_t st) {
+    const int rpb = 16;
+    const dim3 grid(n_tok, (W + rpb - 1) / rpb), block(128);
+    const size_t smem = sizeof(float) * (size_t)top * ff;
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_rows_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return dk_launch(moe_down_rows_kernel<T, VEC>, grid, block, smem, st, (const T*)mid, (const T*)wd, idx, wt, (const T*)shared,
+                     sgate, (T*)out, W, ff, top, rpb);
 }
 
 DK_EXPORT int dk_moe_up_rows(int dtype, const void* x, int W, const void* wgu, const int* idx, void* mid, int ff, int top,
                              int n_tok, int act, cudaStream_t st) {
-    const int rpb = 32;
-    const dim3 grid(n_tok * top, (ff + rpb - 1) / rpb), block(128);
-    const size_t smem = sizeof(float) * (size_t)W;
-    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    if (dtype == 0) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return dk_launch(moe_up_rows_kernel<float>, grid, block, smem, st, (const float*)x, W, (const float*)wgu, idx,
-                         (float*)mid, ff, top, rpb, act);
-    }
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return dk_launch(moe_up_rows_kernel<bf16>, grid, block, smem, st, (const bf16*)x, W, (const bf16*)wgu, idx, (bf16*)mid,
-                     ff, top, rpb, act);
+    const bool vec = (uintptr_t)wgu % 16 == 0 && W % (dtype == 0 ? 4 : 8) == 0;
+    if (dtype == 0)
+        return vec ? launch_up<float, true>(x, W, wgu, idx, mid, ff, top, n_tok, act, st)
+                   : launch_up<float, false>(x, W, wgu, idx, mid, ff, top, n_tok, act, st);
+    return vec ? launch_up<bf16, true>(x, W, wgu, idx, mid, ff, top, n_tok, act, st)
+               : launch_up<bf16, false>(x, W, wgu, idx, mid, ff, top, n_tok, act, st);
 }
 
 DK_EXPORT int dk_moe_down_rows(int dtype, const void* mid, const void* wd, const int* idx, const float* wt,
                                const void* shared, const float* sgate, void* out, int W, int ff, int top, int n_tok,
                                cudaStream_t st) {
-    const int rpb = 32;
-    const dim3 grid(n_tok, (W + rpb - 1) / rpb), block(128);
-    const size_t smem = sizeof(float) * (size_t)top * ff;
-    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    if (dtype == 0) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return dk_launch(moe_down_rows_kernel<float>, grid, block, smem, st, (const float*)mid, (const float*)wd, idx, wt,
-                         (const float*)shared, sgate, (float*)out, W, ff, top, rpb);
-    }
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_down_rows_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return dk_launch(moe_down_rows_kernel<bf16>, grid, block, smem, st, (const bf16*)mid, (const bf16*)wd, idx, wt,
-                     (const bf16*)shared, sgate, (bf16*)out, W, ff, top, rpb);
+    const bool vec = (uintptr_t)wd % 16 == 0 && ff % (dtype == 0 ? 4 : 8) == 0;
+    if (dtype == 0)
+        return vec ? launch_down<float, true>(mid, wd, idx, wt, shared, sgate, out, W, ff, top, n_tok, st)
+                   : launch_down<float, false>(mid, wd, idx, wt, shared, sgate, out, W, ff, top, n_tok, st);
+    return vec ? launch_down<bf16, true>(mid, wd, idx, wt, shared, sgate, out, W, ff, top, n_tok, st)
+               : launch_down<bf16, false>(mid, wd, idx, wt, shared, sgate, out, W, ff, top, n_tok, st);
 }

@@ -13,7 +13,8 @@
 
 #define MT_ROWS 64      // pairs a tile
 #define MT_COLS 64      // output columns a block
-#define MT_KC 32        // inner elements a stage
+#define MT_KC 64        // inner elements a stage: 128 bytes of every row
+#define MT_STAGES 3
 #define MT_STR (MT_KC + 8)
 
 __device__ __forceinline__ void mt_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -73,13 +74,16 @@ moe_sort_kernel(const int* idx, int P, int E, int* perm, int* inv, int* tiles, i
 
 // Block (tile, 64 columns of the output). GATED: B is an expert's [gate rows; up rows] (2 * N rows of K), the
 // output act(gate) * up; A rows are gathered (row r of the tile is token perm[first + r] / top of x). Otherwise B is
-// the expert's [N rows of K] and A the rows first + r of a dense matrix. K % 32 == 0; rows on 16-byte boundaries.
+// the expert's [N rows of K] and A the rows first + r of a dense matrix. K % 64 == 0; rows on 16-byte boundaries.
+// Three stages of 64 inner elements in flight (cp.async), one block barrier a stage.
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* tiles, const int* perm, int top, bf16* out,
                         int N, int K, int act) {
-    __shared__ __align__(16) bf16 As[2][MT_ROWS * MT_STR];
-    __shared__ __align__(16) bf16 Bs[2][(GATED ? 2 : 1) * MT_COLS * MT_STR];
+    extern __shared__ __align__(16) bf16 mt_smem[];
+    constexpr int A_ELEMS = MT_ROWS * MT_STR, B_ELEMS = (GATED ? 2 : 1) * MT_COLS * MT_STR;
+    bf16* As = mt_smem;                              // [MT_STAGES][A_ELEMS]
+    bf16* Bs = mt_smem + MT_STAGES * A_ELEMS;        // [MT_STAGES][B_ELEMS]
     __shared__ int arow[MT_ROWS];
     pdl_wait();
     pdl_launch_dependents();
@@ -90,21 +94,23 @@ moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* ti
     const int n0 = blockIdx.y * MT_COLS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid < MT_ROWS) arow[tid] = tid < rows ? (GATED ? perm[first + tid] / top : first + tid) : -1;
-    for (int i = tid; i < 2 * MT_ROWS * MT_STR / 8; i += 128) reinterpret_cast<uint4*>(&As[0][0])[i] = make_uint4(0u, 0u, 0u, 0u);
-    for (int i = tid; i < 2 * (GATED ? 2 : 1) * MT_COLS * MT_STR / 8; i += 128)
-        reinterpret_cast<uint4*>(&Bs[0][0])[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < MT_STAGES * (A_ELEMS + B_ELEMS) / 8; i += 128) reinterpret_cast<uint4*>(mt_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     const bf16* Be = B + (size_t)e * (GATED ? 2 : 1) * N * K;
-    auto load = [&](int kc, int buf) {
-        const int k0 = kc * MT_KC;
-        for (int i = tid; i < MT_ROWS * 4; i += 128) {             // 4 pieces of 8 elements a row
-            const int r = i >> 2, c = (i & 3) * 8;
-            if (arow[r] >= 0) mt_cp16(&As[buf][r * MT_STR + c], A + (size_t)arow[r] * K + k0 + c);
-        }
-        for (int i = tid; i < (GATED ? 2 : 1) * MT_COLS * 4; i += 128) {
-            const int r = i >> 2, c = (i & 3) * 8;
-            const int n = n0 + (r % MT_COLS);
-            if (n < N) mt_cp16(&Bs[buf][r * MT_STR + c], Be + ((size_t)(r / MT_COLS) * N + n) * K + k0 + c);
+    const int nk = K / MT_KC;
+    constexpr int PCS = MT_KC / 8;                                  // 16-byte pieces a row and stage
+    auto load = [&](int kc) {                                       // stage kc into buffer kc % MT_STAGES; past the end: an empty group
+        if (kc < nk) {
+            const int k0 = kc * MT_KC, buf = kc % MT_STAGES;
+            for (int i = tid; i < MT_ROWS * PCS; i += 128) {
+                const int r = i / PCS, c = (i % PCS) * 8;
+                if (arow[r] >= 0) mt_cp16(As + buf * A_ELEMS + r * MT_STR + c, A + (size_t)arow[r] * K + k0 + c);
+            }
+            for (int i = tid; i < (GATED ? 2 : 1) * MT_COLS * PCS; i += 128) {
+                const int r = i / PCS, c = (i % PCS) * 8;
+                const int n = n0 + (r % MT_COLS);
+                if (n < N) mt_cp16(Bs + buf * B_ELEMS + r * MT_STR + c, Be + ((size_t)(r / MT_COLS) * N + n) * K + k0 + c);
+            }
         }
         mt_commit();
     };
@@ -113,36 +119,33 @@ moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* ti
     for (int i = 0; i < 8; i++) accg[i][0] = accg[i][1] = accg[i][2] = accg[i][3] = 0.f;
 #pragma unroll
     for (int i = 0; i < (GATED ? 8 : 1); i++) accu[i][0] = accu[i][1] = accu[i][2] = accu[i][3] = 0.f;
-    const int nk = K / MT_KC;
-    load(0, 0);
+    load(0);
+    load(1);
     const int j = lane >> 3;
     for (int kc = 0; kc < nk; kc++) {
-        const int buf = kc & 1;
-        if (kc + 1 < nk) {
-            load(kc + 1, buf ^ 1);
-            mt_wait<1>();
-        } else {
-            mt_wait<0>();
-        }
-        __syncthreads();
+        const int buf = kc % MT_STAGES;
+        mt_wait<1>();                 // stage kc has landed (one later group may still be on its way)
+        __syncthreads();              // ... for every thread, and all are done with the buffer that stage kc + 2 goes to
+        load(kc + 2);
+        const bf16* Ab = As + buf * A_ELEMS;
+        const bf16* Bb = Bs + buf * B_ELEMS;
 #pragma unroll
         for (int kk = 0; kk < MT_KC / 16; kk++) {
             uint32_t a[4];
-            mt_ldsm(a, &As[buf][(warp * 16 + (lane & 15)) * MT_STR + kk * 16 + 8 * (lane >> 4)]);
+            mt_ldsm(a, Ab + (warp * 16 + (lane & 15)) * MT_STR + kk * 16 + 8 * (lane >> 4));
 #pragma unroll
             for (int np = 0; np < 4; np++) {
                 uint32_t b[4];
-                mt_ldsm(b, &Bs[buf][(np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1)]);
+                mt_ldsm(b, Bb + (np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1));
                 mt_mma(accg[2 * np], a, b[0], b[1]);
                 mt_mma(accg[2 * np + 1], a, b[2], b[3]);
                 if (GATED) {
-                    mt_ldsm(b, &Bs[buf][(MT_COLS + np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1)]);
+                    mt_ldsm(b, Bb + (MT_COLS + np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1));
                     mt_mma(accu[2 * np], a, b[0], b[1]);
                     mt_mma(accu[2 * np + 1], a, b[2], b[3]);
                 }
             }
         }
-        __syncthreads();
     }
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -185,14 +188,28 @@ DK_EXPORT int dk_moe_sort(const int* idx, int P, int E, int* perm, int* inv, int
 DK_EXPORT int dk_moe_up_tiles(const void* x, const void* wgu, const int* tiles, int max_tiles, const int* perm, int top, void* mid,
                               int ff, int W, int act, cudaStream_t st) {
     if (W % MT_KC || ((uintptr_t)x | (uintptr_t)wgu) % 16) return (int)cudaErrorInvalidValue;
-    return dk_launch(moe_tile_product_kernel<true>, dim3(max_tiles, (ff + MT_COLS - 1) / MT_COLS), dim3(128), 0, st, (const bf16*)x,
+    constexpr size_t smem = sizeof(bf16) * MT_STAGES * (MT_ROWS + 2 * MT_COLS) * MT_STR;
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(moe_tile_product_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr = true;
+    }
+    return dk_launch(moe_tile_product_kernel<true>, dim3(max_tiles, (ff + MT_COLS - 1) / MT_COLS), dim3(128), smem, st, (const bf16*)x,
                      (const bf16*)wgu, tiles, perm, top, (bf16*)mid, ff, W, act);
 }
 
 DK_EXPORT int dk_moe_down_tiles(const void* mid, const void* wd, const int* tiles, int max_tiles, void* y, int W, int ff,
                                 cudaStream_t st) {
     if (ff % MT_KC || ((uintptr_t)mid | (uintptr_t)wd) % 16) return (int)cudaErrorInvalidValue;
-    return dk_launch(moe_tile_product_kernel<false>, dim3(max_tiles, (W + MT_COLS - 1) / MT_COLS), dim3(128), 0, st, (const bf16*)mid,
+    constexpr size_t smem = sizeof(bf16) * MT_STAGES * (MT_ROWS + MT_COLS) * MT_STR;
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(moe_tile_product_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr = true;
+    }
+    return dk_launch(moe_tile_product_kernel<false>, dim3(max_tiles, (W + MT_COLS - 1) / MT_COLS), dim3(128), smem, st, (const bf16*)mid,
                      (const bf16*)wd, tiles, (const int*)nullptr, 1, (bf16*)y, W, ff, 0);
 }
 

@@ -2,7 +2,8 @@
 
 forward = one fused projection [q; k; v; gate; a1] -> the decay's second step z = W_a2 (a1 rows) in float32
 -> the recurrence S <- diag(alpha) S + k v^T, o = S^T q with alpha = sigmoid(z + b)^(1/tau), state and decay in
-float32 (the state lives in the cache's state storage) -> per head an RMS norm over the value size, times
+float32 (the state lives in the cache's state storage; a warp per 8 value columns keeps its part of the state in
+registers for key sizes of 32, 64, 128 and 256, a block form serves the others) -> per head an RMS norm over the value size, times
 silu(gate) -> output projection. Like the other mixers it can be a branch of a ``ParallelMixer`` (``mix``).
 """
 import torch
@@ -63,11 +64,11 @@ class GatedLinearAttention(Part):
         z = linear(a1, self.w_a2, STORE_F32)                      # float32 rows: they enter the recurrence
         o = torch.empty((ctx.n_tok, self.n_mid), dtype=torch.float32, device=self.rt.device)
         if ctx.is_decode:      # one token a row; padding rows carry position -1
-            api.gated_linear_attention_step(q, k, v, o, state, None, ctx.row_pos, ctx.seq_slot, z, self.z_bias, s.tau,
-                                            self.q_scale, ctx.n_tok, s.num_heads, s.head_dim, s.v_head_dim)
+            api.gated_linear_attention(q, k, v, o, state, None, ctx.row_pos, ctx.seq_slot, z, self.z_bias, s.tau,
+                                       self.q_scale, ctx.n_tok, s.num_heads, s.head_dim, s.v_head_dim)
         else:
-            api.gated_linear_attention_step(q, k, v, o, state, ctx.cu_q, ctx.seq_pos0, ctx.seq_slot, z, self.z_bias, s.tau,
-                                            self.q_scale, ctx.n_seq, s.num_heads, s.head_dim, s.v_head_dim)
+            api.gated_linear_attention(q, k, v, o, state, ctx.cu_q, ctx.seq_pos0, ctx.seq_slot, z, self.z_bias, s.tau,
+                                       self.q_scale, ctx.n_seq, s.num_heads, s.head_dim, s.v_head_dim)
         api.norm_gate(o, self.norm_weight, s.norm_eps, gate, scale, mid, group=s.v_head_dim, gate_act="silu")
 
     def forward(self, ctx, views, a, writes=True):
