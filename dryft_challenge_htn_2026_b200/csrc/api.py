@@ -306,6 +306,7 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
 
 # ---------------------------------------------------------------------------------------- products
 MODE_STORE, MODE_STORE_F32, MODE_SILU, MODE_XIELU = 0, 1, 2, 3
+GATE_GELU = (1.0, 0.0)      # ``act`` of a MODE_SILU product whose gate goes through the tanh form of GELU instead of SiLU
 
 
 def sgemm(x, w, out, mode=MODE_STORE, act=(0.0, 0.0)):
@@ -472,7 +473,8 @@ def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None, act=(0.0, 0.0)):
         _tc_err = torch.zeros(1, dtype=torch.int32, device=x.device)
     lib = _lib("gemm_tc.cu")
     _check(lib, lib.dk_gemm_tc(_p(x), _p(w), _p(None if ws is not None else out), M, N, K,
-                               MODE_STORE if mode == MODE_STORE_F32 else mode, _p(_tc_err), sk, _p(ws), bn, int(xielu),
+                               MODE_STORE if mode == MODE_STORE_F32 else mode, _p(_tc_err), sk, _p(ws), bn,
+                               2 if (mode == MODE_SILU and act[0] > 0.5) else int(xielu),
                                c_float(act[0]), c_float(act[1]), _stream()),
            "gemm_tc")
     return Partial(ws) if sk > 1 else out

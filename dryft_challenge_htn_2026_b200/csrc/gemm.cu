@@ -3,7 +3,7 @@
 //
 //  * sgemm: true float32 on CUDA cores (FMA, no tensor-core mode), any M, N, K. Each output is
 //    one sequential sum over K, so a row's result does not depend on the other rows of the batch.
-//    Epilogues: 0/1 store, 2 W = [gate; up]: store silu(gate)*up.
+//    Epilogues: 0/1 store, 2 W = [gate; up]: store silu(gate)*up (with act_pos = 1: the tanh form of GELU instead of SiLU).
 //  * sum_partials: adds up the float32 partial sums of a split-K bfloat16 product for a consumer
 //    that cannot do it while it reads.
 #include "common.cuh"
@@ -13,6 +13,9 @@
 #define SG_BN 64
 #define SG_BK 16
 
+// The gate of a gated product: v * sigmoid(a) with a = v for SiLU, and a = 2 sqrt(2/pi) (v + 0.044715 v^3) for the tanh
+// form of GELU (0.5 v (1 + tanh(u)) = v sigmoid(2u)).
+__device__ __forceinline__ float gate_arg(float v, bool gelu) { return gelu ? 1.5957691216057308f * v * fmaf(0.044715f * v, v, 1.f) : v; }
 template <bool SILU, bool XIELU>
 __global__ void __launch_bounds__(256)
 sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int N, int K, float act_pos, float act_neg) {
@@ -63,7 +66,7 @@ sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int
             const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
             if (m < M && n < N) {
                 float v = acc[i][j];
-                if (SILU) v = v / (1.f + expf(-v)) * acu[i][j];
+                if (SILU) v = v / (1.f + expf(-gate_arg(v, act_pos > 0.5f))) * acu[i][j];   // act_pos 1: GELU gate
                 if (XIELU) v = xielu_f(v, act_pos, act_neg);
                 out[(size_t)m * N + n] = v;
             }
@@ -74,7 +77,7 @@ sgemm_kernel(const float* x, const float* __restrict__ W, float* out, int M, int
 DK_EXPORT int dk_sgemm(const float* x, const float* W, float* out, int M, int N, int K, int mode, float act_pos, float act_neg,
                        cudaStream_t st) {
     dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
-    if (mode == 2) return dk_launch(sgemm_kernel<true, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, 0.f, 0.f);
+    if (mode == 2) return dk_launch(sgemm_kernel<true, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, act_pos, 0.f);
     if (mode == 3) return dk_launch(sgemm_kernel<false, true>, grid, dim3(256), 0, st, x, W, out, M, N, K, act_pos, act_neg);
     return dk_launch(sgemm_kernel<false, false>, grid, dim3(256), 0, st, x, W, out, M, N, K, 0.f, 0.f);
 }

@@ -139,13 +139,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // qk_norm_rope_write, without the rounding to bfloat16 in between; q goes to q_out [M, nh*hd], k
 // and v to the token's place in the paged cache (not when write_kv == 0). Rows with position < 0
 // are padding: nothing is stored for them.
+// The gate of a gated product: v * sigmoid(a) with a = v for SiLU, and a = 2 sqrt(2/pi) (v + 0.044715 v^3) for the tanh
+// form of GELU (0.5 v (1 + tanh(u)) = v sigmoid(2u)).
+__device__ __forceinline__ float gate_arg(float v, bool gelu) { return gelu ? 1.5957691216057308f * v * fmaf(0.044715f * v, v, 1.f) : v; }
 struct QkvEpilogue {
     bf16 *q_out, *k_store, *v_store;
     const float *qn, *kn, *cos_t, *sin_t;
     const int *row_pos, *row_seq, *page_table;
     int pt_stride, nh, nkv, hd, write_kv;
     float eps;
-    // mode 0 only: an activation on the finished sums before they are stored (never on partial sums): 1 = xIELU
+    // an activation on the finished sums before they are stored (never on partial sums): mode 0: 1 = xIELU;
+    // mode 2: 2 = the gate through the tanh form of GELU instead of SiLU
     int act;
     float act_pos, act_neg;
 };
@@ -494,10 +498,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         float4 f = *reinterpret_cast<const float4*>(stg + r * LD + c);
                         if (MODE == 2) {
                             const float4 up = *reinterpret_cast<const float4*>(stg + r * LD + OUT_COLS + c);
-                            f.x = __fdividef(f.x, 1.f + __expf(-f.x)) * up.x;   // 2 ulp: far below the bf16 rounding that follows
-                            f.y = __fdividef(f.y, 1.f + __expf(-f.y)) * up.y;
-                            f.z = __fdividef(f.z, 1.f + __expf(-f.z)) * up.z;
-                            f.w = __fdividef(f.w, 1.f + __expf(-f.w)) * up.w;
+                            const bool gelu = qe.act == 2;
+                            f.x = __fdividef(f.x, 1.f + __expf(-gate_arg(f.x, gelu))) * up.x;   // 2 ulp: far below the bf16 rounding that follows
+                            f.y = __fdividef(f.y, 1.f + __expf(-gate_arg(f.y, gelu))) * up.y;
+                            f.z = __fdividef(f.z, 1.f + __expf(-gate_arg(f.z, gelu))) * up.z;
+                            f.w = __fdividef(f.w, 1.f + __expf(-gate_arg(f.w, gelu))) * up.w;
                         }
                         if (MODE == 0 && qe.act == 1 && ws == nullptr) {
                             f.x = xielu_f(f.x, qe.act_pos, qe.act_neg), f.y = xielu_f(f.y, qe.act_pos, qe.act_neg);
@@ -546,7 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     // step made this epilogue 10 us longer
                     if (row < M) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) f[i] = __fdividef(f[i], 1.f + __expf(-f[i])) * __uint_as_float(u[i]);   // 2 ulp: far below the bf16 rounding that follows
+                        for (int i = 0; i < 32; i++) f[i] = __fdividef(f[i], 1.f + __expf(-gate_arg(f[i], qe.act == 2))) * __uint_as_float(u[i]);   // 2 ulp: far below the bf16 rounding that follows
                     }
                 }
                 if (MODE == 0 && qe.act == 1 && ws == nullptr && row < M) {
@@ -672,9 +677,10 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
 // float32). bn: weight rows a tile, a multiple of 16 from 128 to 256 (mode 2: half of them gate
 // rows, half up rows): the planner picks the height whose tiles and slices load the SMs most evenly.
 // act = 1 (mode 0, SK = 1, bfloat16 out): xIELU with the two constants on the sums before they are stored.
+// act = 2 (mode 2): the gate goes through the tanh form of GELU instead of SiLU.
 DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, int SK, float* ws,
                          int bn, int act, float act_pos, float act_neg, cudaStream_t st) {
-    if (act != 0 && (act != 1 || mode != 0 || SK != 1 || ws != nullptr)) return (int)cudaErrorInvalidValue;
+    if (act != 0 && !(act == 1 && mode == 0 && SK == 1 && ws == nullptr) && !(act == 2 && mode == 2)) return (int)cudaErrorInvalidValue;
     QkvEpilogue qe{};
     qe.act = act, qe.act_pos = act_pos, qe.act_neg = act_neg;
     if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr || SK < 1) return (int)cudaErrorInvalidValue;
@@ -683,7 +689,7 @@ DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, 
     if (SK > 1 && (mode != 0 || ws == nullptr || (SK - 1) * k_per >= k_blocks)) return (int)cudaErrorInvalidValue;
     if (ws != nullptr && mode != 0) return (int)cudaErrorInvalidValue;
 #define TILE_HEIGHT(BN)                                                                                          \
-    if (bn == BN && mode == 2) return launch<BN, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st); \
+    if (bn == BN && mode == 2) return launch<BN, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st, qe); \
     if (bn == BN && mode == 0) return launch<BN, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st, qe)
     TILE_HEIGHT(128); TILE_HEIGHT(144); TILE_HEIGHT(160); TILE_HEIGHT(176); TILE_HEIGHT(192);
     TILE_HEIGHT(208); TILE_HEIGHT(224); TILE_HEIGHT(240); TILE_HEIGHT(256);

@@ -80,6 +80,9 @@ __host__ __device__ constexpr size_t smem_bytes(int warps, int mr, int slice) {
 // gridDim.x is a multiple of SK: block b has slice b % SK and tiles b / SK, + gridDim.x / SK, ...
 // (Dealing the rows out evenly instead, in tiles of unequal heights, was measured 15 % slower: the
 // bytes a ring slot holds in flight shrink with the tile, and the kernel lives on bytes in flight.)
+// The gate of a gated product: v * sigmoid(a) with a = v for SiLU, and a = 2 sqrt(2/pi) (v + 0.044715 v^3) for the tanh
+// form of GELU (0.5 v (1 + tanh(u)) = v sigmoid(2u)).
+__device__ __forceinline__ float gate_arg(float v, bool gelu) { return gelu ? 1.5957691216057308f * v * fmaf(0.044715f * v, v, 1.f) : v; }
 template <int MR, int MODE, int WARPS>
 __global__ void __launch_bounds__((WARPS + 1) * 32)
 gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK, int tiles,
@@ -186,7 +189,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
                         float up = 0.f;
 #pragma unroll
                         for (int w = 0; w < WARPS; w++) up += sums[w * (WR * MR) + (8 + i) * MR + j];
-                        v = v / (1.f + expf(-v)) * up;
+                        v = v / (1.f + expf(-gate_arg(v, act_pos > 0.5f))) * up;   // act_pos 1: GELU gate
                     }
                     if (MODE == 3) v = xielu_f(v, act_pos, act_neg);
                     if (SK > 1) ws[((size_t)slice * M + j) * N + n] = v;
@@ -281,6 +284,7 @@ DK_EXPORT long long dk_gemv_stream_smem(int rows, int K, int SK, int warps) {
 // multiple of SK; `warps` streaming warps a block, 4 or 8. Refused (cudaErrorInvalidValue) when the
 // rows of a slice do not fit the shared memory of a block of that shape.
 // Mode 3: as mode 0 with xIELU (constants act_pos, act_neg) on the sums before they are stored; SK = 1.
+// Mode 2 with act_pos = 1: the gate goes through the tanh form of GELU instead of SiLU.
 DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws, int M, int N, int K, int mode, int SK,
                              int blocks, int warps, float act_pos, float act_neg, cudaStream_t st) {
     if (M < 1 || M > 16 || K % 16 != 0 || SK < 1 || blocks < SK || (warps != 4 && warps != 8)) return (int)cudaErrorInvalidValue;
@@ -292,7 +296,7 @@ DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws,
     if (mode == 0) return launch<MR, 0, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);        \
     if (mode == 1) return launch<MR, 1, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);        \
     if (mode == 3) return launch<MR, 3, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st, act_pos, act_neg); \
-    return launch<MR, 2, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st);
+    return launch<MR, 2, WARPS>(xp, wp, out, ws, M, N, K, SK, blocks, st, act_pos, 0.f);
 #define GS_CASE(MR)                   \
     if (warps == 4) { GS_MODE(MR, 4) } \
     GS_MODE(MR, 8)

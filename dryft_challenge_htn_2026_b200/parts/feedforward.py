@@ -34,12 +34,9 @@ class GatedMLP(Part):
         return [self.w_gate_up, self.w_down]
 
     def forward(self, ctx, a):
-        if self.spec.activation == "silu":
-            return linear(linear(a, self.w_gate_up, SILU), self.w_down, allow_partial=True)
-        gu = linear(a, self.w_gate_up)
-        mid = torch.empty((gu.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
-        api.act_mul(gu, mid, api.ACT_GELU_TANH)
-        return linear(mid, self.w_down, allow_partial=True)
+        # the activation and the product with the up rows sit in the epilogue of every product kernel
+        act = api.GATE_GELU if self.spec.activation == "gelu_tanh" else (0.0, 0.0)
+        return linear(linear(a, self.w_gate_up, SILU, act=act), self.w_down, allow_partial=True)
 
 
 register_part(GatedMLPSpec, GatedMLP)

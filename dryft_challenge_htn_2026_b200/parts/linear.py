@@ -15,7 +15,8 @@ STORE, STORE_F32, SILU, XIELU = api.MODE_STORE, api.MODE_STORE_F32, api.MODE_SIL
 
 def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
     """mode STORE: [M, N] in x's dtype; STORE_F32: float32 (logits); SILU: w = [gate; up] rows,
-    returns silu(x.gate^T) * (x.up^T) of width N/2; XIELU: xielu(x.w^T) with the constants ``act`` =
+    returns silu(x.gate^T) * (x.up^T) of width N/2 (with ``act`` = ``api.GATE_GELU`` the gate goes through the tanh
+    form of GELU instead); XIELU: xielu(x.w^T) with the constants ``act`` =
     (alpha_pos, alpha_neg), in the product's epilogue wherever the product is this library's (after
     the library's product a row kernel applies it). ``allow_partial``: the caller can take
     ``csrc.api.Partial`` (split-K partial sums, added up by the kernel that consumes them) instead
@@ -34,7 +35,7 @@ def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
         out = torch.mm(x, w.t())
         if mode == SILU:
             half = torch.empty((M, N), dtype=x.dtype, device=x.device)
-            api.silu_mul(out, half)
+            api.act_mul(out, half, api.ACT_GELU_TANH if act[0] > 0.5 else api.ACT_SILU)
             return half
         if mode == XIELU:
             api.xielu(out, out, act[0], act[1])
@@ -50,7 +51,7 @@ def linear(x, w, mode=STORE, allow_partial=False, act=(0.0, 0.0)):
     if mode == STORE_F32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     if mode == SILU:
-        return api.gemm_tc(x, w, mode, None, api.gated_tc_plan(M, N))   # TMA + tcgen05, SiLU*up fused into the epilogue
+        return api.gemm_tc(x, w, mode, None, api.gated_tc_plan(M, N), act)   # TMA + tcgen05, SiLU*up fused into the epilogue
     if api.gemm_tc_fills_gpu(M, N):
         return api.gemm_tc(x, w, mode, act=act)
     out = torch.mm(x, w.t())
