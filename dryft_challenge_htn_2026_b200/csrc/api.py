@@ -1060,11 +1060,12 @@ def conv_state_update(proj, state, taps, cu_q, seq_pos0, seq_slot, n_seq):
 MOE_MAX_EXPERTS = 256
 
 
-def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, idx, wt, shared_gate):
+def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, idx, wt, shared_gate, scores=None):
     """Router of a mixture of experts, float32 arithmetic: s = sigmoid(w_router x); the ``top`` experts with the
     largest s + correction among the ``keep`` best of ``groups`` groups of neighbours (group score: its two
     largest s + correction) -> ``idx`` int32 [T, top]; ``wt`` float32 [T, top] = their s over the sum, times
-    ``scale``; ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given."""
+    ``scale``; ``shared_gate`` float32 [T] = sigmoid(w_shared_gate . x) when that vector is given. Two kernels: the
+    scores (``scores`` float32 [T, E], scratch), then the choice."""
     _need(x, "x", None, 2), _need(w_router, "w_router", torch.float32, 2), _need(correction, "correction", torch.float32, 1)
     _need(w_shared_gate, "w_shared_gate", torch.float32, 1), _need(idx, "idx", torch.int32, 2), _need(wt, "wt", torch.float32, 2)
     _need(shared_gate, "shared_gate", torch.float32, 1)
@@ -1074,9 +1075,15 @@ def moe_route(x, w_router, correction, w_shared_gate, top, groups, keep, scale, 
             not 1 <= keep <= groups or not 1 <= top <= min(E, 32) or (correction is not None and correction.numel() != E) or \
             (w_shared_gate is not None and (w_shared_gate.numel() != W or shared_gate is None or shared_gate.numel() != T)):
         raise KernelError("moe_route: shapes do not match (up to 256 experts, up to 32 chosen)")
+    if scores is None:
+        scores = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    _need(scores, "scores", torch.float32, 2)
+    if scores.shape != (T, E):
+        raise KernelError("moe_route: scores must be float32 [tokens, experts]")
     lib = _lib("moe.cu")
     _check(lib, lib.dk_moe_route(_dt(x), _p(x), W, _p(w_router), _p(correction), _p(w_shared_gate), E, int(top), int(groups),
-                                 int(keep), c_float(scale), _p(idx), _p(wt), _p(shared_gate), T, _stream()), "moe_route")
+                                 int(keep), c_float(scale), _p(idx), _p(wt), _p(shared_gate), _p(scores), T, _stream()),
+           "moe_route", 2)
 
 
 def moe_up_rows(x, w_gate_up, idx, mid, act=0):

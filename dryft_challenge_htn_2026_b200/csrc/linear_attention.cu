@@ -222,46 +222,78 @@ gla_warp_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     }
 }
 
-// The same with the rows staged: the block's four warps share a head, so its q, k and decay rows (and the block's 32
-// value columns) of 16 tokens at a time come into shared memory by cp.async, two stages in turn, and the warps read
-// them from there: the loads of the next 16 tokens run under the arithmetic of these. Rows on 16-byte boundaries.
+// The same with the rows staged: the block's warps share a head, so its q, k and decay rows (and the block's value
+// columns) of 16 tokens at a time come into shared memory by cp.async, two stages in turn, and the warps read them
+// from there: the loads of the next 16 tokens run under the arithmetic of these. A warp takes VC = 8, 4 or 2 value
+// columns and a block BC = 32 or 16 of them: a single sequence of few heads is cut fine, so that every scheduler of
+// every SM has a warp or two (one warp alone waits out every shuffle of its folds). Rows on 16-byte boundaries.
 #define GLA_NT 16
 __device__ __forceinline__ void gla_cp16(void* smem, const void* gmem) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
 }
-template <typename T, int DPL>
-__global__ void __launch_bounds__(128)
+// the VC column sums of the 32 lanes: halves are exchanged while more than one value is left, then plain sums; lane l
+// ends with the sum of the column whose number is spelled by its top log2(VC) bits
+template <int VC> __device__ __forceinline__ float fold_columns(const float (&o)[VC], int lane) {
+    float r;
+    if (VC == 8) {
+        const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+        float r4[4], r2[2];
+#pragma unroll
+        for (int c = 0; c < 4; c++) r4[c] = (h16 ? o[(4 + c) % VC] : o[c % VC]) + __shfl_xor_sync(0xffffffffu, h16 ? o[c % VC] : o[(4 + c) % VC], 16);
+#pragma unroll
+        for (int c = 0; c < 2; c++) r2[c] = (h8 ? r4[2 + c] : r4[c]) + __shfl_xor_sync(0xffffffffu, h8 ? r4[c] : r4[2 + c], 8);
+        r = (h4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, h4 ? r2[0] : r2[1], 4);
+    } else if (VC == 4) {
+        const bool h16 = lane & 16, h8 = lane & 8;
+        float r2[2];
+#pragma unroll
+        for (int c = 0; c < 2; c++) r2[c] = (h16 ? o[(2 + c) % VC] : o[c % VC]) + __shfl_xor_sync(0xffffffffu, h16 ? o[c % VC] : o[(2 + c) % VC], 16);
+        r = (h8 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, h8 ? r2[0] : r2[1], 8);
+        r += __shfl_xor_sync(0xffffffffu, r, 4);
+    } else {
+        const bool h16 = lane & 16;
+        r = (h16 ? o[1 % VC] : o[0]) + __shfl_xor_sync(0xffffffffu, h16 ? o[0] : o[1 % VC], 16);
+        r += __shfl_xor_sync(0xffffffffu, r, 8);
+        r += __shfl_xor_sync(0xffffffffu, r, 4);
+    }
+    r += __shfl_xor_sync(0xffffffffu, r, 2);
+    r += __shfl_xor_sync(0xffffffffu, r, 1);
+    return r;
+}
+template <typename T, int DPL, int VC>
+__global__ void __launch_bounds__(512)
 gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
                        const float* __restrict__ alpha, float* __restrict__ out, float* state, const int* cu_q,
-                       const int* seq_pos0, const int* seq_slot, int nh, int hdv, float q_scale) {
+                       const int* seq_pos0, const int* seq_slot, int nh, int hdv, float q_scale, int BC) {
     constexpr int HDK = 32 * DPL;
     constexpr int QB = GLA_NT * HDK * (int)sizeof(T), AB = GLA_NT * HDK * 4, VB = GLA_NT * 32 * (int)sizeof(T);
     constexpr int STAGE = 2 * QB + AB + VB;
+    constexpr int WRITERS = 32 / VC;                  // every WRITERS-th lane holds a column's sum
     extern __shared__ __align__(16) unsigned char gla_smem[];
     pdl_wait();
     pdl_launch_dependents();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, threads = blockDim.x;
     const int s = blockIdx.x, h = blockIdx.y;
-    const int col0 = blockIdx.z * 32, c0 = col0 + warp * 8;
+    const int col0 = blockIdx.z * BC, c0 = col0 + warp * VC;
     const bool active = c0 < hdv;
-    const int cols_here = min(32, hdv - col0);
+    const int cols_here = min(BC, hdv - col0);
     const int r0 = cu_q ? cu_q[s] : s, r1 = cu_q ? cu_q[s + 1] : s + 1;
     const size_t ow = (size_t)nh * hdv;
-    const int my_col = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    const int my_col = lane / WRITERS;
     if (seq_pos0[s] < 0) {
-        if (active && (lane & 3) == 0)
+        if (active && lane % WRITERS == 0)
             for (int t = r0; t < r1; t++) out[(size_t)t * ow + (size_t)h * hdv + c0 + my_col] = 0.f;
         return;
     }
     float* S = state + ((size_t)seq_slot[s] * nh + h) * (size_t)HDK * hdv + (size_t)(DPL * lane) * hdv + c0;
-    float st[DPL][8];
+    float st[DPL][VC];
 #pragma unroll
     for (int i = 0; i < DPL; i++) {
-        if (active) ld_vec<8>(S + (size_t)i * hdv, st[i], true);
+        if (active) ld_vec<VC>(S + (size_t)i * hdv, st[i], VC >= 4);
         else
 #pragma unroll
-            for (int c = 0; c < 8; c++) st[i][c] = 0.f;
+            for (int c = 0; c < VC; c++) st[i][c] = 0.f;
     }
     const int n_chunks = (r1 - r0 + GLA_NT - 1) / GLA_NT;
     constexpr int QP = HDK * (int)sizeof(T) / 16, AP = HDK * 4 / 16;         // 16-byte pieces a token
@@ -270,18 +302,18 @@ gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         if (c < n_chunks) {
             unsigned char* base = gla_smem + (c & 1) * STAGE;
             const int t0 = r0 + c * GLA_NT, nt = min(GLA_NT, r1 - t0);
-            for (int i = tid; i < nt * QP; i += 128) {
+            for (int i = tid; i < nt * QP; i += threads) {
                 const int tt = i / QP, pc = i % QP;
                 const size_t src = ((size_t)(t0 + tt) * ld + (size_t)h * HDK) * sizeof(T) + pc * 16;
                 gla_cp16(base + tt * (HDK * sizeof(T)) + pc * 16, reinterpret_cast<const unsigned char*>(q) + src);
                 gla_cp16(base + QB + tt * (HDK * sizeof(T)) + pc * 16, reinterpret_cast<const unsigned char*>(k) + src);
             }
-            for (int i = tid; i < nt * AP; i += 128) {
+            for (int i = tid; i < nt * AP; i += threads) {
                 const int tt = i / AP, pc = i % AP;
                 gla_cp16(base + 2 * QB + tt * (HDK * 4) + pc * 16,
                          reinterpret_cast<const unsigned char*>(alpha + (size_t)(t0 + tt) * nh * HDK + (size_t)h * HDK) + pc * 16);
             }
-            for (int i = tid; i < nt * VP; i += 128) {
+            for (int i = tid; i < nt * VP; i += threads) {
                 const int tt = i / VP, pc = i % VP;
                 gla_cp16(base + 2 * QB + AB + tt * (32 * sizeof(T)) + pc * 16,
                          reinterpret_cast<const unsigned char*>(v + (size_t)(t0 + tt) * ld + (size_t)h * hdv + col0) + pc * 16);
@@ -289,7 +321,6 @@ gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
     issue(0);
     for (int c = 0; c < n_chunks; c++) {
         issue(c + 1);
@@ -304,44 +335,34 @@ gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         if (active) {
 #pragma unroll 4
             for (int tt = 0; tt < nt; tt++) {     // unrolled: one token's folds run under the next tokens' multiply-adds
-                float qv[DPL], kv[DPL], av[DPL], vv[8];
+                float qv[DPL], kv[DPL], av[DPL], vv[VC];
                 ld_vec<DPL>(sq + tt * HDK + DPL * lane, qv, true);
                 ld_vec<DPL>(sk + tt * HDK + DPL * lane, kv, true);
                 ld_vec<DPL>(sa + tt * HDK + DPL * lane, av, true);
-                ld_vec<8>(sv + tt * 32 + warp * 8, vv, true);
-                float o[8];
+                ld_vec<VC>(sv + tt * 32 + warp * VC, vv, true);
+                float o[VC];
 #pragma unroll
-                for (int cc = 0; cc < 8; cc++) o[cc] = 0.f;
+                for (int cc = 0; cc < VC; cc++) o[cc] = 0.f;
 #pragma unroll
                 for (int i = 0; i < DPL; i++) {
                     const float qs = qv[i] * q_scale;
 #pragma unroll
-                    for (int cc = 0; cc < 8; cc++) {
+                    for (int cc = 0; cc < VC; cc++) {
                         st[i][cc] = fmaf(av[i], st[i][cc], kv[i] * vv[cc]);
                         o[cc] = fmaf(st[i][cc], qs, o[cc]);
                     }
                 }
-                float r4[4], r2[2], r;
-#pragma unroll
-                for (int cc = 0; cc < 4; cc++)
-                    r4[cc] = (hi16 ? o[4 + cc] : o[cc]) + __shfl_xor_sync(0xffffffffu, hi16 ? o[cc] : o[4 + cc], 16);
-#pragma unroll
-                for (int cc = 0; cc < 2; cc++)
-                    r2[cc] = (hi8 ? r4[2 + cc] : r4[cc]) + __shfl_xor_sync(0xffffffffu, hi8 ? r4[cc] : r4[2 + cc], 8);
-                r = (hi4 ? r2[1] : r2[0]) + __shfl_xor_sync(0xffffffffu, hi4 ? r2[0] : r2[1], 4);
-                r += __shfl_xor_sync(0xffffffffu, r, 2);
-                r += __shfl_xor_sync(0xffffffffu, r, 1);
-                if ((lane & 3) == 0) out[(size_t)(t0 + tt) * ow + (size_t)h * hdv + c0 + my_col] = r;
+                const float r = fold_columns<VC>(o, lane);
+                if (lane % WRITERS == 0) out[(size_t)(t0 + tt) * ow + (size_t)h * hdv + c0 + my_col] = r;
             }
         }
         __syncthreads();              // the stage is free for the chunk after next
     }
     if (active) {
 #pragma unroll
-        for (int i = 0; i < DPL; i++) {
-            *reinterpret_cast<float4*>(S + (size_t)i * hdv) = make_float4(st[i][0], st[i][1], st[i][2], st[i][3]);
-            *reinterpret_cast<float4*>(S + (size_t)i * hdv + 4) = make_float4(st[i][4], st[i][5], st[i][6], st[i][7]);
-        }
+        for (int i = 0; i < DPL; i++)
+#pragma unroll
+            for (int c = 0; c < VC; c++) S[(size_t)i * hdv + c] = st[i][c];
     }
 }
 
@@ -355,15 +376,26 @@ static int launch_gla_warp(const void* q, const void* k, const void* v, long lon
         return dk_launch(gla_warp_kernel<T, D>, grid, block, 0, st, (const T*)q, (const T*)k, (const T*)v, ld, alpha, out, \
                          state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale, vec);
     if (vec && n_tok_max > 4) {      // portions: staged rows (single tokens have nothing to run ahead of)
-#define GLA_STAGED(D)                                                                                                      \
-    if (hd == 32 * D) {                                                                                                    \
+        // columns a warp and a block: coarse when the sequences and heads alone fill the schedulers, finer when not
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long blocks32 = (long long)n_seq * nh * ((hdv + 31) / 32), scheds = 4LL * sms;
+        int VCs = 8, BC = 32;
+        if (blocks32 * 4 < 3 * scheds) VCs = 4;
+        if (blocks32 * 8 < 3 * scheds) { VCs = 2; if (blocks32 < sms) BC = 16; }
+        const dim3 sgrid(n_seq, nh, (hdv + BC - 1) / BC), sblock(32 * BC / VCs);
+#define GLA_STAGED(D, V)                                                                                                   \
+    if (hd == 32 * D && VCs == V) {                                                                                        \
         const size_t smem = 2 * (size_t)(2 * GLA_NT * 32 * D * sizeof(T) + GLA_NT * 32 * D * 4 + GLA_NT * 32 * sizeof(T));  \
         if (smem > 48 * 1024)                                                                                              \
-            cudaFuncSetAttribute(gla_warp_staged_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-        return dk_launch(gla_warp_staged_kernel<T, D>, grid, block, smem, st, (const T*)q, (const T*)k, (const T*)v, ld,   \
-                         alpha, out, state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale);                                   \
+            cudaFuncSetAttribute(gla_warp_staged_kernel<T, D, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        return dk_launch(gla_warp_staged_kernel<T, D, V>, sgrid, sblock, smem, st, (const T*)q, (const T*)k, (const T*)v,  \
+                         ld, alpha, out, state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale, BC);                           \
     }
-        GLA_STAGED(1) GLA_STAGED(2) GLA_STAGED(4) GLA_STAGED(8)
+        GLA_STAGED(1, 8) GLA_STAGED(2, 8) GLA_STAGED(4, 8) GLA_STAGED(8, 8)
+        GLA_STAGED(1, 4) GLA_STAGED(2, 4) GLA_STAGED(4, 4) GLA_STAGED(8, 4)
+        GLA_STAGED(1, 2) GLA_STAGED(2, 2) GLA_STAGED(4, 2) GLA_STAGED(8, 2)
 #undef GLA_STAGED
     }
     GLA_WARP(1) GLA_WARP(2) GLA_WARP(4) GLA_WARP(8)

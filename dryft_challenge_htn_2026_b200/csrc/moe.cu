@@ -27,71 +27,91 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-// A block routes up to ROUTE_TOKENS tokens: their rows sit in shared memory, each of the 8 warps takes every 8th
-// expert and works out its logit for all the block's tokens at once (the router's row is read once a block, 16 bytes
-// a lane where the width allows), then warp t makes the choice for token t.
+// The router in two kernels. Scores: block (8 tokens, 8 experts), the tokens' rows in shared memory, a warp an expert
+// (the row after the last expert is the shared expert's gate): its row of the router is read once for the 8 tokens, 16
+// bytes a lane where the width allows; sigmoid of the float32 sums -> scores [tokens, experts] (and the gate).
 template <typename T>
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
-moe_route_kernel(const T* x, int W, const float* __restrict__ wr, const float* __restrict__ corr,
-                 const float* __restrict__ wsg, int E, int top, int groups, int keep, float scale, int* idx, float* wt,
-                 float* sgate, int n_tok, int tokens_per_block) {
+moe_scores_kernel(const T* x, int W, const float* __restrict__ wr, const float* __restrict__ wsg, int E, float* scores,
+                  float* sgate, int n_tok) {
     extern __shared__ __align__(16) unsigned char route_smem[];
-    float* s_all = reinterpret_cast<float*>(route_smem);                 // [tokens][E] sigmoid scores
-    float* c_all = s_all + tokens_per_block * E;                         // [tokens][E] choice scores
-    float* g_all = c_all + tokens_per_block * E;                         // [tokens][E] group scores
-    T* xs = reinterpret_cast<T*>(g_all + tokens_per_block * E);          // [tokens][W]
+    T* xs = reinterpret_cast<T*>(route_smem);          // [ROUTE_TOKENS][W]
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int t0 = blockIdx.x * tokens_per_block;
-    const int nt = min(tokens_per_block, n_tok - t0);
-    for (int i = threadIdx.x; i < nt * W; i += blockDim.x) xs[i] = x[(size_t)t0 * W + i];
-    __syncthreads();
-    const bool vec = W % 4 == 0;
-    for (int e = w; e <= E; e += ROUTE_WARPS) {         // e == E: the shared expert's gate
-        const float* row = e < E ? wr + (size_t)e * W : wsg;
-        if (row == nullptr) continue;
-        float acc[ROUTE_TOKENS];
-#pragma unroll
-        for (int tt = 0; tt < ROUTE_TOKENS; tt++) acc[tt] = 0.f;
-        if (vec) {
-#pragma unroll 2
-            for (int k = lane * 4; k < W; k += 128) {
-                const float4 r = __ldg(reinterpret_cast<const float4*>(row + k));
-#pragma unroll
-                for (int tt = 0; tt < ROUTE_TOKENS; tt++)
-                    if (tt < nt) {
-                        const T* xr = xs + tt * W + k;
-                        acc[tt] = fmaf(r.x, to_f(xr[0]), fmaf(r.y, to_f(xr[1]), fmaf(r.z, to_f(xr[2]), fmaf(r.w, to_f(xr[3]), acc[tt]))));
-                    }
-            }
-        } else {
-            for (int k = lane; k < W; k += 32)
-#pragma unroll
-                for (int tt = 0; tt < ROUTE_TOKENS; tt++)
-                    if (tt < nt) acc[tt] = fmaf(row[k], to_f(xs[tt * W + k]), acc[tt]);
-        }
-#pragma unroll
-        for (int tt = 0; tt < ROUTE_TOKENS; tt++) {
-            if (tt >= nt) continue;
-            const float z = warp_sum(acc[tt]);
-            if (lane == 0) {
-                const float sg = 1.f / (1.f + expf(-z));
-                if (e < E) {
-                    s_all[tt * E + e] = sg;
-                    c_all[tt * E + e] = sg + (corr ? corr[e] : 0.f);
-                } else {
-                    sgate[t0 + tt] = sg;
-                }
-            }
-        }
+    const int t0 = blockIdx.x * ROUTE_TOKENS;
+    const int nt = min(ROUTE_TOKENS, n_tok - t0);
+    const int e = blockIdx.y * ROUTE_WARPS + w;
+    const bool vec = W % 8 == 0;
+    if (vec) {
+        const int pieces = nt * W * (int)sizeof(T) / 16;
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t0 * W);
+        for (int i = threadIdx.x; i < pieces; i += blockDim.x) reinterpret_cast<uint4*>(xs)[i] = src[i];
+    } else {
+        for (int i = threadIdx.x; i < nt * W; i += blockDim.x) xs[i] = x[(size_t)t0 * W + i];
     }
     __syncthreads();
-    if (w >= nt) return;
-    const int t = t0 + w;
-    float* s = s_all + w * E;
-    float* c = c_all + w * E;
-    float* gs = g_all + w * E;
+    const float* row = e < E ? wr + (size_t)e * W : (e == E ? wsg : nullptr);
+    if (row == nullptr) return;
+    float acc[ROUTE_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < ROUTE_TOKENS; tt++) acc[tt] = 0.f;
+    if (vec) {
+#pragma unroll 4
+        for (int k = lane * 4; k < W; k += 128) {
+            const float4 r = __ldg(reinterpret_cast<const float4*>(row + k));
+#pragma unroll
+            for (int tt = 0; tt < ROUTE_TOKENS; tt++)
+                if (tt < nt) {
+                    float xv[4];
+                    if (sizeof(T) == 2) {
+                        const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(xs) + tt * W + k);
+                        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+                        xv[0] = a.x, xv[1] = a.y, xv[2] = b.x, xv[3] = b.y;
+                    } else {
+                        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(xs) + tt * W + k);
+                        xv[0] = a.x, xv[1] = a.y, xv[2] = a.z, xv[3] = a.w;
+                    }
+                    acc[tt] = fmaf(r.x, xv[0], fmaf(r.y, xv[1], fmaf(r.z, xv[2], fmaf(r.w, xv[3], acc[tt]))));
+                }
+        }
+    } else {
+        for (int k = lane; k < W; k += 32)
+#pragma unroll
+            for (int tt = 0; tt < ROUTE_TOKENS; tt++)
+                if (tt < nt) acc[tt] = fmaf(row[k], to_f(xs[tt * W + k]), acc[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < ROUTE_TOKENS; tt++) {
+        if (tt >= nt) continue;
+        const float z = warp_sum(acc[tt]);
+        if (lane == 0) {
+            const float sg = 1.f / (1.f + expf(-z));
+            if (e < E) scores[(size_t)(t0 + tt) * E + e] = sg;
+            else sgate[t0 + tt] = sg;
+        }
+    }
+}
+
+// Choice: a warp a token, from the token's scores.
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_choose_kernel(const float* scores, const float* __restrict__ corr, int E, int top, int groups, int keep, float scale,
+                  int* idx, float* wt, int n_tok) {
+    extern __shared__ __align__(16) unsigned char route_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int t = blockIdx.x * ROUTE_WARPS + w;
+    if (t >= n_tok) return;
+    float* s = reinterpret_cast<float*>(route_smem) + (size_t)w * 3 * E;
+    float* c = s + E;
+    float* gs = c + E;
+    for (int e = lane; e < E; e += 32) {
+        s[e] = scores[(size_t)t * E + e];
+        c[e] = s[e] + (corr ? corr[e] : 0.f);
+    }
+    __syncwarp();
     if (groups > 1 && keep < groups) {
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {       // a group's score: its two largest choice scores
@@ -257,25 +277,29 @@ moe_down_rows_kernel(const T* mid, const T* __restrict__ wd, const int* idx, con
 }
 
 template <typename T>
-static int launch_route(const void* x, int W, const float* wr, const float* corr, const float* wsg, int E, int top, int groups,
-                        int keep, float scale, int* idx, float* wt, float* sgate, int n_tok, cudaStream_t st) {
-    int tpb = ROUTE_TOKENS;
-    auto need = [&](int t) { return sizeof(float) * 3 * (size_t)t * E + sizeof(T) * (size_t)t * W; };
-    while (tpb > 1 && need(tpb) > 160 * 1024) tpb >>= 1;
-    const size_t smem = need(tpb);
+static int launch_scores(const void* x, int W, const float* wr, const float* wsg, int E, float* scores, float* sgate, int n_tok,
+                         cudaStream_t st) {
+    const size_t smem = sizeof(T) * (size_t)ROUTE_TOKENS * W;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return dk_launch(moe_route_kernel<T>, dim3((n_tok + tpb - 1) / tpb), dim3(32 * ROUTE_WARPS), smem, st, (const T*)x, W, wr, corr,
-                     wsg, E, top, groups, keep, scale, idx, wt, sgate, n_tok, tpb);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_scores_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int rows = E + (wsg != nullptr ? 1 : 0);
+    return dk_launch(moe_scores_kernel<T>, dim3((n_tok + ROUTE_TOKENS - 1) / ROUTE_TOKENS, (rows + ROUTE_WARPS - 1) / ROUTE_WARPS),
+                     dim3(32 * ROUTE_WARPS), smem, st, (const T*)x, W, wr, wsg, E, scores, sgate, n_tok);
 }
 
+// scores: float32 scratch [n_tok, E]
 DK_EXPORT int dk_moe_route(int dtype, const void* x, int W, const float* wr, const float* corr, const float* wsg, int E,
-                           int top, int groups, int keep, float scale, int* idx, float* wt, float* sgate, int n_tok,
+                           int top, int groups, int keep, float scale, int* idx, float* wt, float* sgate, float* scores, int n_tok,
                            cudaStream_t st) {
-    if (E < 1 || E > MOE_MAX_EXPERTS || top < 1 || top > 32 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups)
+    if (E < 1 || E > MOE_MAX_EXPERTS || top < 1 || top > 32 || top > E || groups < 1 || E % groups || keep < 1 || keep > groups ||
+        scores == nullptr || (sizeof(float) * ROUTE_TOKENS * W > 200 * 1024))
         return (int)cudaErrorInvalidValue;
-    if (dtype == 0) return launch_route<float>(x, W, wr, corr, wsg, E, top, groups, keep, scale, idx, wt, sgate, n_tok, st);
-    return launch_route<bf16>(x, W, wr, corr, wsg, E, top, groups, keep, scale, idx, wt, sgate, n_tok, st);
+    int e = dtype == 0 ? launch_scores<float>(x, W, wr, wsg, E, scores, sgate, n_tok, st)
+                       : launch_scores<bf16>(x, W, wr, wsg, E, scores, sgate, n_tok, st);
+    if (e) return e;
+    const size_t smem = sizeof(float) * 3 * (size_t)E * ROUTE_WARPS;
+    return dk_launch(moe_choose_kernel, dim3((n_tok + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(32 * ROUTE_WARPS), smem, st, scores, corr,
+                     E, top, groups, keep, scale, idx, wt, n_tok);
 }
 
 template <typename T, bool VEC>

@@ -114,11 +114,18 @@ moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* ti
         }
         mt_commit();
     };
-    float accg[8][4], accu[GATED ? 8 : 1][4];
+    // four warps as 2 x 2: each owns 32 rows x 32 columns (two 16-row fragments of A against two 16-column fragments
+    // of B: 6 ldmatrix for 16 mma a 16-wide step of the gated product, where 16 x 64 a warp needed 9)
+    const int wm = warp >> 1, wn = warp & 1;
+    float accg[2][4][4], accu[GATED ? 2 : 1][4][4];
 #pragma unroll
-    for (int i = 0; i < 8; i++) accg[i][0] = accg[i][1] = accg[i][2] = accg[i][3] = 0.f;
+    for (int m = 0; m < 2; m++)
 #pragma unroll
-    for (int i = 0; i < (GATED ? 8 : 1); i++) accu[i][0] = accu[i][1] = accu[i][2] = accu[i][3] = 0.f;
+        for (int i = 0; i < 4; i++) accg[m][i][0] = accg[m][i][1] = accg[m][i][2] = accg[m][i][3] = 0.f;
+#pragma unroll
+    for (int m = 0; m < (GATED ? 2 : 1); m++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) accu[m][i][0] = accu[m][i][1] = accu[m][i][2] = accu[m][i][3] = 0.f;
     load(0);
     load(1);
     const int j = lane >> 3;
@@ -131,39 +138,46 @@ moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* ti
         const bf16* Bb = Bs + buf * B_ELEMS;
 #pragma unroll
         for (int kk = 0; kk < MT_KC / 16; kk++) {
-            uint32_t a[4];
-            mt_ldsm(a, Ab + (warp * 16 + (lane & 15)) * MT_STR + kk * 16 + 8 * (lane >> 4));
+            uint32_t a0[4], a1[4];
+            mt_ldsm(a0, Ab + (wm * 32 + (lane & 15)) * MT_STR + kk * 16 + 8 * (lane >> 4));
+            mt_ldsm(a1, Ab + (wm * 32 + 16 + (lane & 15)) * MT_STR + kk * 16 + 8 * (lane >> 4));
 #pragma unroll
-            for (int np = 0; np < 4; np++) {
+            for (int np = 0; np < 2; np++) {
                 uint32_t b[4];
-                mt_ldsm(b, Bb + (np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1));
-                mt_mma(accg[2 * np], a, b[0], b[1]);
-                mt_mma(accg[2 * np + 1], a, b[2], b[3]);
+                mt_ldsm(b, Bb + (wn * 32 + np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1));
+                mt_mma(accg[0][2 * np], a0, b[0], b[1]);
+                mt_mma(accg[0][2 * np + 1], a0, b[2], b[3]);
+                mt_mma(accg[1][2 * np], a1, b[0], b[1]);
+                mt_mma(accg[1][2 * np + 1], a1, b[2], b[3]);
                 if (GATED) {
-                    mt_ldsm(b, Bb + (MT_COLS + np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1));
-                    mt_mma(accu[2 * np], a, b[0], b[1]);
-                    mt_mma(accu[2 * np + 1], a, b[2], b[3]);
+                    mt_ldsm(b, Bb + (MT_COLS + wn * 32 + np * 16 + (lane & 7) + 8 * (j >> 1)) * MT_STR + kk * 16 + 8 * (j & 1));
+                    mt_mma(accu[0][2 * np], a0, b[0], b[1]);
+                    mt_mma(accu[0][2 * np + 1], a0, b[2], b[3]);
+                    mt_mma(accu[1][2 * np], a1, b[0], b[1]);
+                    mt_mma(accu[1][2 * np + 1], a1, b[2], b[3]);
                 }
             }
         }
     }
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
+    for (int m = 0; m < 2; m++)
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const int r = warp * 16 + g + 8 * (c >> 1), n = n0 + nt * 8 + 2 * t + (c & 1);
-            if (r < rows && n < N) {
-                float v = accg[nt][c];
-                if (GATED) {
-                    const float u = accu[nt][c];
-                    v = (act == 1 ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
-                                  : v / (1.f + expf(-v))) * u;
+        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int r = wm * 32 + m * 16 + g + 8 * (c >> 1), n = n0 + wn * 32 + nt * 8 + 2 * t + (c & 1);
+                if (r < rows && n < N) {
+                    float v = accg[m][nt][c];
+                    if (GATED) {
+                        const float u = accu[m][nt][c];
+                        v = (act == 1 ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                                      : v / (1.f + expf(-v))) * u;
+                    }
+                    out[(size_t)(first + r) * N + n] = __float2bfloat16_rn(v);
                 }
-                out[(size_t)(first + r) * N + n] = __float2bfloat16_rn(v);
             }
         }
-    }
 }
 
 // out[t][c] = sum_j wt[t][j] * y[inv[t * top + j]][c] + sgate[t] * shared[t][c]
