@@ -70,10 +70,11 @@ SHAPES = {
               layers=[attn(2, 1, 64, 64, 3, 0.125, 20.0, (32, 250000.0), (100, 5), {"kind": "dense", "ff": 192}),
                       gla(2, 64, 64, 16.0, moe(8, 64, 2, 2, 2, 2.5, 64)),
                       attn(2, 2, 128, 128, 3, 0.09, 50.0, (128, 10000.0), None, {"kind": "dense", "ff": 160})]),
-    # sizes that no tensor-core kernel takes: heads of 20 / 10 / 24 / 12, an expert size of 20, a decay rank of 5
+    # sizes that no tensor-core kernel takes: heads of 20 / 10 / 24 / 12, an expert size of 20, a dense feed-forward of
+    # 52 (no multiple of 8), a decay rank of 5
     "D": dict(architecture="Pibulix", vocab=136, width=48, norm={"eps": 1e-5}, postln_alpha=1.5, decay_rank=[None, 5],
               layers=[attn(3, 1, 20, 10, 3, 0.22, 8.0, (10, 100.0), (33, 2), moe(3, 20, 2, 3, 2, 1.0, 20)),
-                      gla(1, 24, 12, 2.0, {"kind": "dense", "ff": 56})]),
+                      gla(1, 24, 12, 2.0, {"kind": "dense", "ff": 52})]),
 }
 
 
