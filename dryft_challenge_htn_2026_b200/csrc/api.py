@@ -1017,13 +1017,14 @@ SHORT_CONV_MAX_TAPS = 9
 
 
 def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos, sin, rot_dims, row_pos, row_seq, seq_pos0,
-                   seq_slot, n_heads, n_kv_heads, head_dim, v_head_dim):
+                   seq_slot, n_heads, n_kv_heads, head_dim, v_head_dim, k_store=None, v_store=None, page_table=None):
     """Rows [q | k | v] of a fused projection -> ``out`` rows of the same layout: a causal convolution of
     ``taps`` taps over time on every channel (``w_conv`` [channels, taps]; earlier rows of the same step, or
     the sequence's ``state`` [slots, taps-1, channels] for positions before it), then per q and k head an RMS
     norm with weights of the head's size, then the rotate-half rotation of the first ``rot_dims`` coordinates
     by cos/sin [positions, rot_dims/2]. Each step optional (taps 1, weights None, rot_dims 0). The state is
-    only read: ``conv_state_update`` moves it on afterwards."""
+    only read: ``conv_state_update`` moves it on afterwards. With ``k_store`` / ``v_store`` [pages, nkv, PAGE, size] and
+    ``page_table`` the k and v heads also go to each token's place in the paged cache."""
     _need_rows(proj, "proj"), _need_rows(out, "out", proj.dtype)
     C = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
     _need(state, "state", proj.dtype, 3), _need(w_conv, "w_conv", proj.dtype, 2)
@@ -1037,11 +1038,17 @@ def conv_norm_rope(proj, out, state, w_conv, taps, q_norm_w, k_norm_w, eps, cos,
             max(head_dim, v_head_dim) > 256 or (q_norm_w is not None and q_norm_w.numel() != head_dim) or \
             (k_norm_w is not None and k_norm_w.numel() != head_dim):
         raise KernelError("conv_norm_rope: shapes do not match")
+    if k_store is not None:
+        _need(k_store, "k_store", proj.dtype, 4), _need(v_store, "v_store", proj.dtype, 4), _need(page_table, "page_table", torch.int32, 2)
+        if k_store.shape[1:] != (n_kv_heads, PAGE, head_dim) or v_store.shape[1:] != (n_kv_heads, PAGE, v_head_dim):
+            raise KernelError("conv_norm_rope: key/value stores of the wrong shape")
     lib = _lib("short_conv.cu")
     _check(lib, lib.dk_conv_norm_rope(_dt(proj), _p(proj), c_longlong(proj.stride(0)), _p(out), c_longlong(out.stride(0)),
                                       _p(state), _p(w_conv), int(taps), _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos),
                                       _p(sin), int(rot_dims), _p(row_pos), _p(row_seq), _p(seq_pos0), _p(seq_slot),
-                                      proj.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, _stream()), "conv_norm_rope")
+                                      proj.shape[0], n_heads, n_kv_heads, head_dim, v_head_dim, _p(k_store), _p(v_store),
+                                      _p(page_table), page_table.shape[1] if page_table is not None else 0, _stream()),
+           "conv_norm_rope")
 
 
 def conv_state_update(proj, state, taps, cu_q, seq_pos0, seq_slot, n_seq):

@@ -7,7 +7,8 @@
 //   * a rotate-half rotation of the first rot_dims coordinates of each query and key head (coordinate i
 //     with i + rot_dims / 2) by angles from a table [positions, rot_dims / 2]; the rest pass.
 // Each option may be left out (taps = 1, no norm weights, rot_dims = 0). The result is a dense row
-// [q heads | k heads | v heads] in the storage type; sums, norms and the rotation are float32.
+// [q heads | k heads | v heads] in the storage type; sums, norms and the rotation are float32. Given the paged
+// key and value stores, the kernel also writes each token's k and v heads to their place there (the step's cache write).
 // A second kernel moves the state on once the first has read it.
 #include "common.cuh"
 
@@ -20,7 +21,8 @@ __global__ void __launch_bounds__(SC_THREADS)
 conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const T* state, const T* __restrict__ wconv,
                       int taps, const float* __restrict__ qn, const float* __restrict__ kn, float eps,
                       const float* __restrict__ cosv, const float* __restrict__ sinv, int rot_dims, const int* row_pos,
-                      const int* row_seq, const int* seq_pos0, const int* seq_slot, int nh, int nkv, int hd, int hdv) {
+                      const int* row_seq, const int* seq_pos0, const int* seq_slot, int nh, int nkv, int hd, int hdv,
+                      T* k_store, T* v_store, const int* page_table, int pt_stride) {
     __shared__ float red[33];
     __shared__ float ys[256];
     pdl_wait();
@@ -86,10 +88,22 @@ conv_norm_rope_kernel(const T* proj, long long ld, T* out, long long ldo, const 
             }
         }
     }
+    // k and v heads also go to the token's place in the paged stores when those are given (the cache write of the step)
+    T* cached = nullptr;
+    if (k_store != nullptr && head >= nh) {
+        const int page = page_table[(size_t)s * pt_stride + pos / DK_PAGE];
+        if (page >= 0)
+            cached = head < nh + nkv ? k_store + kv_offset(page, nkv, head - nh, pos % DK_PAGE, hd)
+                                     : v_store + kv_offset(page, nkv, head - nh - nkv, pos % DK_PAGE, hdv);
+    }
 #pragma unroll
     for (int r = 0; r < 2; r++) {
         const int d = threadIdx.x + r * SC_THREADS;
-        if (d < size) out[(size_t)t * ldo + c0 + d] = from_f<T>(y[r]);
+        if (d < size) {
+            const T o = from_f<T>(y[r]);
+            out[(size_t)t * ldo + c0 + d] = o;
+            if (cached != nullptr) cached[d] = o;
+        }
     }
 }
 
@@ -122,17 +136,18 @@ DK_EXPORT int dk_conv_norm_rope(int dtype, const void* proj, long long ld, void*
                                 const void* wconv, int taps, const float* qn, const float* kn, float eps,
                                 const float* cosv, const float* sinv, int rot_dims, const int* row_pos,
                                 const int* row_seq, const int* seq_pos0, const int* seq_slot, int n_tok, int nh, int nkv,
-                                int hd, int hdv, cudaStream_t st) {
+                                int hd, int hdv, void* k_store, void* v_store, const int* page_table, int pt_stride,
+                                cudaStream_t st) {
     if (hd > 256 || hdv > 256 || taps < 1 || taps > SC_MAX_TAPS || rot_dims > hd || rot_dims % 2)
         return (int)cudaErrorInvalidValue;
     const dim3 grid(n_tok, nh + 2 * nkv), block(SC_THREADS);
     if (dtype == 0)
         return dk_launch(conv_norm_rope_kernel<float>, grid, block, 0, st, (const float*)proj, ld, (float*)out, ldo,
                          (const float*)state, (const float*)wconv, taps, qn, kn, eps, cosv, sinv, rot_dims, row_pos,
-                         row_seq, seq_pos0, seq_slot, nh, nkv, hd, hdv);
+                         row_seq, seq_pos0, seq_slot, nh, nkv, hd, hdv, (float*)k_store, (float*)v_store, page_table, pt_stride);
     return dk_launch(conv_norm_rope_kernel<bf16>, grid, block, 0, st, (const bf16*)proj, ld, (bf16*)out, ldo,
                      (const bf16*)state, (const bf16*)wconv, taps, qn, kn, eps, cosv, sinv, rot_dims, row_pos, row_seq,
-                     seq_pos0, seq_slot, nh, nkv, hd, hdv);
+                     seq_pos0, seq_slot, nh, nkv, hd, hdv, (bf16*)k_store, (bf16*)v_store, page_table, pt_stride);
 }
 
 DK_EXPORT int dk_conv_state_update(int dtype, const void* proj, long long ld, void* state, int taps, int C,

@@ -121,7 +121,7 @@ class MaskedAttention(Part):
 
     def prepared_rows(self, ctx, views, proj, writes=True):
         """[q | k | v] of the projection rows after the convolution, the head norm and the rotation, as a dense
-        matrix; the convolution's state moves on behind it."""
+        matrix; with ``writes`` the k and v heads also go into the cache; the convolution's state moves on behind it."""
         s = self.spec
         if not writes and self.taps > 1:
             raise ValueError("a layer with a short convolution cannot run on another layer's cache entry")
@@ -136,7 +136,9 @@ class MaskedAttention(Part):
         qkv = proj[:, :self.n_qkv]
         api.conv_norm_rope(qkv, out, state, self.w_conv, self.taps, self.q_norm_w, self.k_norm_w,
                            self.qk_norm.eps if self.qk_norm is not None else 0.0, cos, sin, rot, ctx.row_pos, ctx.row_seq,
-                           pos0, ctx.seq_slot, s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim)
+                           pos0, ctx.seq_slot, s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim,
+                           views[0].k if writes else None, views[0].v if writes else None,
+                           ctx.tables[views[0].group] if writes else None)
         if self.taps > 1:
             api.conv_state_update(qkv, state, self.taps, None if ctx.is_decode else ctx.cu_q, pos0, ctx.seq_slot, ctx.n_seq)
         return out
@@ -149,6 +151,7 @@ class MaskedAttention(Part):
         gate = proj[:, self.n_q + self.n_k + self.n_v:] if s.output_gate else None
         if self.prepares:
             proj = self.prepared_rows(ctx, views, proj, writes)
+            writes = False          # that kernel has stored the step's keys and values
         q = proj[:, :self.n_q]
         k = proj[:, self.n_q:self.n_q + self.n_k]
         v = proj[:, self.n_q + self.n_k:self.n_q + self.n_k + self.n_v]
