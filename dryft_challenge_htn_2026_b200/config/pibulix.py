@@ -13,7 +13,9 @@ config.json keys (every size, and every constant that differs between models of 
             | {type: "gla", mixer: {heads, dim, vdim, tau}, mlp: ...}
      with mlp = {kind: "dense", ff} | {kind: "moe", expert: {ff}, router: {experts, top, scale, groups: {count, keep}},
                                        shared: {ff}} | null,
-     and optionally weights_of: j (the layer has no tensors; it runs on layer j's).
+     and optionally weights_of: j (the layer has no tensors; it runs on layer j's; what its entry leaves out is layer j's).
+  Left out: kv_heads = heads, vdim = dim, conv = 1, softcap = none, rot = none, mask = none, keep_first = 0, tau = 1,
+  router.scale = 1, router.groups = one group, postln_alpha = 1.
 Tensors: embed, head, final.norm, and per layer with tensors l<i>.norm1, l<i>.norm2,
   attention: l<i>.mix.{q,k,v,o}, .mix.{q,k,v}.conv [channels, taps], .mix.{q,k}.norm [dim];
   gla: l<i>.mix.{q,k,v,g,o}, .mix.norm [vdim], .mix.a1 [rank, width], .mix.a2 [heads*dim, rank], .mix.a2.b;
@@ -59,10 +61,12 @@ def _check_mlp(mlp, where):
 
 def _check_mixer(kind, m, where):
     if kind == "attention":
-        H, G = get(m, "heads", int, positive=True), get(m, "kv_heads", int, positive=True)
+        H = get(m, "heads", int, positive=True)
+        G = get(m, "kv_heads", int, H, positive=True)          # left out: as many key/value heads as query heads
         if H % G:
             raise ConfigError(f"config.json: {where}: {H} heads are not a multiple of {G} key/value heads")
-        out = {"heads": H, "kv_heads": G, "dim": get(m, "dim", int, positive=True), "vdim": get(m, "vdim", int, positive=True),
+        dim = get(m, "dim", int, positive=True)
+        out = {"heads": H, "kv_heads": G, "dim": dim, "vdim": get(m, "vdim", int, dim, positive=True),
                "conv": get(m, "conv", int, 1, positive=True), "scale": get(m, "scale", float),
                "softcap": get(m, "softcap", float, 0.0)}
         rot = m.get("rot")
@@ -79,8 +83,9 @@ def _check_mixer(kind, m, where):
                 raise ConfigError(f"config.json: {where}.mask.keep_first must not be negative")
         return out
     if kind == "gla":
-        return {"heads": get(m, "heads", int, positive=True), "dim": get(m, "dim", int, positive=True),
-                "vdim": get(m, "vdim", int, positive=True), "tau": get(m, "tau", float, positive=True)}
+        dim = get(m, "dim", int, positive=True)
+        return {"heads": get(m, "heads", int, positive=True), "dim": dim, "vdim": get(m, "vdim", int, dim, positive=True),
+                "tau": get(m, "tau", float, 1.0, positive=True)}
     raise ConfigError(f"config.json: {where}.type {kind!r} is not implemented (attention, gla)")
 
 
@@ -104,6 +109,10 @@ class PibulixConfig(ModelConfig):
         for i, lc in enumerate(layers):
             if not isinstance(lc, dict):
                 raise ConfigError(f"config.json: layers[{i}] must be an object")
+            j = lc.get("weights_of")
+            if isinstance(j, int) and not isinstance(j, bool) and 0 <= j < len(layers) and isinstance(layers[j], dict):
+                # what an entry that runs on another layer's weights leaves out is that layer's
+                lc = dict({k: v for k, v in layers[j].items() if k != "weights_of"}, **lc)
             kind = lc.get("type")
             entry = {"type": kind, "mixer": _check_mixer(kind, _section(lc, "mixer", f"layers[{i}]"), f"layers[{i}].mixer"),
                      "mlp": _check_mlp(lc.get("mlp"), f"layers[{i}]")}

@@ -84,6 +84,18 @@ def test_spec_carries_every_constant():
     assert (m.window, m.keep_first, m.softcap, m.conv_taps, m.position) == (None, 0, None, None, None)
 
 
+def test_what_an_entry_leaves_out():
+    d = copy.deepcopy(BASE)
+    d["layers"][2] = {"weights_of": 0}                       # only the pointer: the rest is layer 0's
+    d["layers"][1] = dict(GLA, mixer={"heads": 3, "dim": 8, "tau": 4.0})
+    d["layers"][4] = dict(d["layers"][1], weights_of=1)
+    d["layers"][0] = dict(ATT, mixer={k: v for k, v in ATT["mixer"].items() if k not in ("kv_heads", "vdim")})
+    cfg = dk.config_from_dict(d)
+    l = cfg.layer_dicts()
+    assert l[2]["mixer"] == l[0]["mixer"] and l[2]["weights_of"] == 0
+    assert l[0]["mixer"]["kv_heads"] == 4 and l[0]["mixer"]["vdim"] == 16 and l[1]["mixer"]["vdim"] == 8
+
+
 def test_tensor_names_and_shapes():
     cfg = dk.config_from_dict(BASE).with_shapes({"l3.mix.a1": (7, 32)})
     decls = CausalLM(cfg.to_spec(), torch.float32, "cpu").param_decls(False)
