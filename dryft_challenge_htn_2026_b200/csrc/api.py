@@ -1125,8 +1125,8 @@ MOE_TILE_ROWS = 64
 
 def moe_tiles_take(x, expert_ff):
     """Whether a step's routed experts run as tiles on the tensor cores: bfloat16, more than 32 tokens, inner
-    sizes (width and expert size) that are multiples of 64."""
-    return x.dtype == torch.bfloat16 and x.shape[0] > 32 and x.shape[1] % 64 == 0 and expert_ff % 64 == 0
+    sizes (width and expert size) that are multiples of 32."""
+    return x.dtype == torch.bfloat16 and x.shape[0] > 32 and x.shape[1] % 32 == 0 and expert_ff % 32 == 0
 
 
 def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, act=0, scratch=None):
@@ -1140,8 +1140,8 @@ def moe_experts_tiles(x, w_gate_up, w_down, idx, wt, shared, shared_gate, out, a
     top = idx.shape[1]
     E, ff = w_down.shape[0], w_down.shape[2]
     if w_gate_up.shape != (E, 2 * ff, W) or w_down.shape[1] != W or idx.shape[0] != T or wt.shape != idx.shape or \
-            out.shape != (T, W) or W % 64 or ff % 64 or E > MOE_MAX_EXPERTS or (shared is not None and shared.shape != (T, W)):
-        raise KernelError("moe_experts_tiles: shapes do not match (inner sizes in steps of 64)")
+            out.shape != (T, W) or W % 32 or ff % 32 or E > MOE_MAX_EXPERTS or (shared is not None and shared.shape != (T, W)):
+        raise KernelError("moe_experts_tiles: shapes do not match (inner sizes in steps of 32)")
     P = T * top
     max_tiles = (P + MOE_TILE_ROWS - 1) // MOE_TILE_ROWS + E
     dev = x.device

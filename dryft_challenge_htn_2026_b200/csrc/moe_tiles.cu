@@ -13,7 +13,7 @@
 
 #define MT_ROWS 64      // pairs a tile
 #define MT_COLS 64      // output columns a block
-#define MT_KC 64        // inner elements a stage: 128 bytes of every row
+#define MT_KC 32        // inner elements a stage
 #define MT_STAGES 3
 #define MT_STR (MT_KC + 8)
 
@@ -74,8 +74,9 @@ moe_sort_kernel(const int* idx, int P, int E, int* perm, int* inv, int* tiles, i
 
 // Block (tile, 64 columns of the output). GATED: B is an expert's [gate rows; up rows] (2 * N rows of K), the
 // output act(gate) * up; A rows are gathered (row r of the tile is token perm[first + r] / top of x). Otherwise B is
-// the expert's [N rows of K] and A the rows first + r of a dense matrix. K % 64 == 0; rows on 16-byte boundaries.
-// Three stages of 64 inner elements in flight (cp.async), one block barrier a stage.
+// the expert's [N rows of K] and A the rows first + r of a dense matrix. K % 32 == 0; rows on 16-byte boundaries.
+// Three stages of 32 inner elements in flight (cp.async), one block barrier a stage: 46 KB a block, four blocks an SM
+// (stages of 64 left room for two blocks and ran 12 % slower).
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_tile_product_kernel(const bf16* A, const bf16* __restrict__ B, const int* tiles, const int* perm, int top, bf16* out,
