@@ -14,6 +14,7 @@
 // serves single-token steps, short portions and every float32 step. Portions of many tokens in bfloat16
 // run in blocks of 64 tokens on the tensor cores (linear_attention_bf16.cu).
 #include "common.cuh"
+#include <type_traits>
 
 #define LA_THREADS 256
 #define LA_TB 8   // tokens staged at a time by the step kernel
@@ -223,8 +224,8 @@ gla_warp_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
 }
 
 // The same with the rows staged: the block's warps share a head, so its q, k and decay rows (and the block's value
-// columns) of 16 tokens at a time come into shared memory by cp.async, two stages in turn, and the warps read them
-// from there: the loads of the next 16 tokens run under the arithmetic of these. A warp takes VC = 8, 4 or 2 value
+// columns) of 16 tokens at a time come into shared memory by cp.async, up to four stages in turn, and the warps read
+// them from there: the loads of the next chunks run under the arithmetic of this one. A warp takes VC = 8, 4 or 2 value
 // columns and a block BC = 32 or 16 of them: a single sequence of few heads is cut fine, so that every scheduler of
 // every SM has a warp or two (one warp alone waits out every shuffle of its folds). Rows on 16-byte boundaries.
 #define GLA_NT 16
@@ -265,7 +266,7 @@ template <typename T, int DPL, int VC>
 __global__ void __launch_bounds__(512)
 gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
                        const float* __restrict__ alpha, float* __restrict__ out, float* state, const int* cu_q,
-                       const int* seq_pos0, const int* seq_slot, int nh, int hdv, float q_scale, int BC) {
+                       const int* seq_pos0, const int* seq_slot, int nh, int hdv, float q_scale, int BC, int n_stages) {
     constexpr int HDK = 32 * DPL;
     constexpr int QB = GLA_NT * HDK * (int)sizeof(T), AB = GLA_NT * HDK * 4, VB = GLA_NT * 32 * (int)sizeof(T);
     constexpr int STAGE = 2 * QB + AB + VB;
@@ -300,7 +301,7 @@ gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
     const int VP = cols_here * (int)sizeof(T) / 16;
     auto issue = [&](int c) {
         if (c < n_chunks) {
-            unsigned char* base = gla_smem + (c & 1) * STAGE;
+            unsigned char* base = gla_smem + (c % n_stages) * STAGE;
             const int t0 = r0 + c * GLA_NT, nt = min(GLA_NT, r1 - t0);
             for (int i = tid; i < nt * QP; i += threads) {
                 const int tt = i / QP, pc = i % QP;
@@ -321,40 +322,62 @@ gla_warp_staged_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    issue(0);
+    // n_stages - 1 chunks ahead: a chunk's arithmetic is shorter than a trip to memory (with one chunk ahead every
+    // chunk waited out that trip: 3 us for 16 tokens, whatever the warps did)
+    for (int c = 0; c < n_stages - 1; c++) issue(c);
     for (int c = 0; c < n_chunks; c++) {
-        issue(c + 1);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        issue(c + n_stages - 1);
+        if (n_stages == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
+        else if (n_stages == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+        else asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
-        const unsigned char* base = gla_smem + (c & 1) * STAGE;
+        const unsigned char* base = gla_smem + (c % n_stages) * STAGE;
         const T* sq = reinterpret_cast<const T*>(base);
         const T* sk = reinterpret_cast<const T*>(base + QB);
         const float* sa = reinterpret_cast<const float*>(base + 2 * QB);
         const T* sv = reinterpret_cast<const T*>(base + 2 * QB + AB);
         const int t0 = r0 + c * GLA_NT, nt = min(GLA_NT, r1 - t0);
         if (active) {
-#pragma unroll 4
-            for (int tt = 0; tt < nt; tt++) {     // unrolled: one token's folds run under the next tokens' multiply-adds
-                float qv[DPL], kv[DPL], av[DPL], vv[VC];
-                ld_vec<DPL>(sq + tt * HDK + DPL * lane, qv, true);
-                ld_vec<DPL>(sk + tt * HDK + DPL * lane, kv, true);
-                ld_vec<DPL>(sa + tt * HDK + DPL * lane, av, true);
-                ld_vec<VC>(sv + tt * 32 + warp * VC, vv, true);
-                float o[VC];
+            // U tokens a turn: their state updates follow one another (one multiply-add each), their folds are
+            // independent chains of five shuffles that run side by side (one token at a time, a warp alone on its
+            // scheduler waited out every shuffle: the time did not depend on the columns a warp took)
+            constexpr int U = DPL * VC <= 16 ? 4 : 2;
+            auto turn = [&](int tt0, auto tail_c) {
+                constexpr bool TAIL = decltype(tail_c)::value;    // the chunk's last turn may hold fewer than U tokens
+                float o[U][VC];
 #pragma unroll
-                for (int cc = 0; cc < VC; cc++) o[cc] = 0.f;
+                for (int u = 0; u < U; u++) {
+                    const int tt = TAIL ? min(tt0 + u, nt - 1) : tt0 + u;   // past the end: the last token again, its result unused
+                    float qv[DPL], kv[DPL], av[DPL], vv[VC];
+                    ld_vec<DPL>(sq + tt * HDK + DPL * lane, qv, true);
+                    ld_vec<DPL>(sk + tt * HDK + DPL * lane, kv, true);
+                    ld_vec<DPL>(sa + tt * HDK + DPL * lane, av, true);
+                    ld_vec<VC>(sv + tt * 32 + warp * VC, vv, true);
+                    const bool live = !TAIL || tt0 + u < nt;
 #pragma unroll
-                for (int i = 0; i < DPL; i++) {
-                    const float qs = qv[i] * q_scale;
+                    for (int cc = 0; cc < VC; cc++) o[u][cc] = 0.f;
 #pragma unroll
-                    for (int cc = 0; cc < VC; cc++) {
-                        st[i][cc] = fmaf(av[i], st[i][cc], kv[i] * vv[cc]);
-                        o[cc] = fmaf(st[i][cc], qs, o[cc]);
+                    for (int i = 0; i < DPL; i++) {
+                        const float qs = qv[i] * q_scale;
+#pragma unroll
+                        for (int cc = 0; cc < VC; cc++) {
+                            const float nx = fmaf(av[i], st[i][cc], kv[i] * vv[cc]);
+                            st[i][cc] = live ? nx : st[i][cc];
+                            o[u][cc] = fmaf(nx, qs, o[u][cc]);
+                        }
                     }
                 }
-                const float r = fold_columns<VC>(o, lane);
-                if (lane % WRITERS == 0) out[(size_t)(t0 + tt) * ow + (size_t)h * hdv + c0 + my_col] = r;
-            }
+                float r[U];
+#pragma unroll
+                for (int u = 0; u < U; u++) r[u] = fold_columns<VC>(o[u], lane);
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if ((!TAIL || tt0 + u < nt) && lane % WRITERS == 0)
+                        out[(size_t)(t0 + tt0 + u) * ow + (size_t)h * hdv + c0 + my_col] = r[u];
+            };
+            int tt0 = 0;
+            for (; tt0 + U <= nt; tt0 += U) turn(tt0, std::false_type{});
+            if (tt0 < nt) turn(tt0, std::true_type{});
         }
         __syncthreads();              // the stage is free for the chunk after next
     }
@@ -387,11 +410,13 @@ static int launch_gla_warp(const void* q, const void* k, const void* v, long lon
         const dim3 sgrid(n_seq, nh, (hdv + BC - 1) / BC), sblock(32 * BC / VCs);
 #define GLA_STAGED(D, V)                                                                                                   \
     if (hd == 32 * D && VCs == V) {                                                                                        \
-        const size_t smem = 2 * (size_t)(2 * GLA_NT * 32 * D * sizeof(T) + GLA_NT * 32 * D * 4 + GLA_NT * 32 * sizeof(T));  \
+        const size_t stage = 2 * GLA_NT * 32 * D * sizeof(T) + GLA_NT * 32 * D * 4 + GLA_NT * 32 * sizeof(T);              \
+        const int n_stages = stage * 4 <= 160 * 1024 ? 4 : (stage * 3 <= 160 * 1024 ? 3 : 2);                              \
+        const size_t smem = n_stages * stage;                                                                              \
         if (smem > 48 * 1024)                                                                                              \
             cudaFuncSetAttribute(gla_warp_staged_kernel<T, D, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         return dk_launch(gla_warp_staged_kernel<T, D, V>, sgrid, sblock, smem, st, (const T*)q, (const T*)k, (const T*)v,  \
-                         ld, alpha, out, state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale, BC);                           \
+                         ld, alpha, out, state, cu_q, seq_pos0, seq_slot, nh, hdv, q_scale, BC, n_stages);                 \
     }
         GLA_STAGED(1, 8) GLA_STAGED(2, 8) GLA_STAGED(4, 8) GLA_STAGED(8, 8)
         GLA_STAGED(1, 4) GLA_STAGED(2, 4) GLA_STAGED(4, 4) GLA_STAGED(8, 4)
